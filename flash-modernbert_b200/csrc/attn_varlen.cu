@@ -1,0 +1,391 @@
+// Varlen (cu_seqlens-confined) non-causal self-attention for head dim 64 on the
+// fused, already-rotated qkv [T, 3*nh*64]: full attention for global layers and a
+// |i-j| <= half_window band for local layers, one kernel family.
+//
+// A small scheduling kernel turns cu_seqlens into a table of query tiles
+// (prefix sum of ceil(len / BM)), so the attention grid depends only on the token
+// and sequence capacities and can be captured in a CUDA graph while the real
+// boundaries stay in device memory.
+//
+// This file holds the register-tiled kernel: NWARPS warps per CTA, 16 query rows
+// per warp, 64-key tiles double-buffered with cp.async, online softmax in fp32 in
+// the exp2 domain, P rounded to bf16 for the P*V product.  NWARPS is chosen from
+// max_seqlen, which gives the short-query tiles that ~30-token sequences want
+// (one 32-row CTA covers a whole sequence) and 64-row tiles otherwise.
+#include <algorithm>
+
+#include "pe_host.h"
+#include "pe_ptx.cuh"
+
+namespace pe {
+
+constexpr int ATT_BN = 64;  // keys per tile
+constexpr int ATT_D = 64;
+
+// tile_start[n] = number of query tiles of sequences 0..n-1; tile_start[n_seqs] = total.
+__global__ void attn_schedule_kernel(const int32_t* __restrict__ cu_seqlens, int n_seqs, int bm,
+                                     int32_t* __restrict__ tile_start) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    carry_s = 0;
+    tile_start[0] = 0;
+  }
+  __syncthreads();
+  for (int base = 0; base < n_seqs; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    int v = 0;
+    if (i < n_seqs) {
+      const int len = cu_seqlens[i + 1] - cu_seqlens[i];
+      v = len > 0 ? (len + bm - 1) / bm : 0;
+    }
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = (lane < (blockDim.x >> 5)) ? warp_sums[lane] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += n;
+      }
+      warp_sums[lane] = w;
+    }
+    __syncthreads();
+    const int warp_off = (warp == 0) ? 0 : warp_sums[warp - 1];
+    const int carry = carry_s;
+    if (i < n_seqs) tile_start[i + 1] = carry + warp_off + incl;
+    __syncthreads();
+    if (threadIdx.x == 0) carry_s = carry + warp_sums[(blockDim.x >> 5) - 1];
+    __syncthreads();
+  }
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                        uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                          uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Byte offset of the 16-byte chunk `chunk` (0..7) of row `row` in a [rows][64] bf16
+// tile whose chunks are XOR-swizzled by the row so ldmatrix reads are conflict free.
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+  return uint32_t(row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+// Loads `rows` rows x 64 bf16 from global (row stride `stride` elements) into a
+// swizzled tile; rows at or beyond `valid_rows` are zero-filled.
+template <int THREADS>
+__device__ __forceinline__ void load_tile_async(uint32_t smem_tile, const __nv_bfloat16* gbase,
+                                                int64_t stride, int rows, int valid_rows) {
+  for (int i = threadIdx.x; i < rows * 8; i += THREADS) {
+    const int r = i >> 3, c = i & 7;
+    const bool ok = r < valid_rows;
+    const __nv_bfloat16* src = gbase + (ok ? int64_t(r) * stride : 0) + c * 8;
+    cp_async16(smem_tile + tile_off(r, c), src, ok ? 16 : 0);
+  }
+}
+
+template <int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
+attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t* __restrict__ cu_seqlens,
+                       const int32_t* __restrict__ tile_start, int n_seqs, int nh, int half_window,
+                       __nv_bfloat16* __restrict__ out) {
+  constexpr int BM = NWARPS * 16;
+  constexpr int THREADS = NWARPS * 32;
+  __shared__ __align__(128) uint8_t smem[BM * 128 + 4 * ATT_BN * 128];
+  const uint32_t sQ = smem_u32(smem);
+  const uint32_t sK = sQ + BM * 128;
+  const uint32_t sV = sK + 2 * ATT_BN * 128;
+
+  const int total_tiles = tile_start[n_seqs];
+  const int tile = blockIdx.x;
+  if (tile >= total_tiles) return;
+  // Sequence owning this tile: last n with tile_start[n] <= tile.
+  int lo = 0, hi = n_seqs;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_start[mid] <= tile) lo = mid; else hi = mid;
+  }
+  const int seq = lo;
+  const int seq_begin = cu_seqlens[seq];
+  const int len = cu_seqlens[seq + 1] - seq_begin;
+  const int q0 = (tile - tile_start[seq]) * BM;
+  const int head = blockIdx.y;
+  const int H = nh * ATT_D;
+  const int64_t stride = 3 * int64_t(H);
+  const __nv_bfloat16* qg = qkv + int64_t(seq_begin) * stride + head * ATT_D;
+  const __nv_bfloat16* kg = qg + H;
+  const __nv_bfloat16* vg = qg + 2 * H;
+
+  int kv_lo = 0, kv_hi = len;
+  if (half_window >= 0) {
+    kv_lo = max(0, q0 - half_window);
+    kv_hi = min(len, q0 + BM + half_window);
+  }
+  const int n_kv = (kv_hi - kv_lo + ATT_BN - 1) / ATT_BN;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  load_tile_async<THREADS>(sQ, qg + int64_t(q0) * stride, stride, BM, len - q0);
+  load_tile_async<THREADS>(sK, kg + int64_t(kv_lo) * stride, stride, ATT_BN, kv_hi - kv_lo);
+  load_tile_async<THREADS>(sV, vg + int64_t(kv_lo) * stride, stride, ATT_BN, kv_hi - kv_lo);
+  cp_async_commit();
+
+  float o_acc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o_acc[j][e] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  uint32_t qf[4][4];
+  const float scale_log2 = 0.125f * 1.4426950408889634f;
+  const int row_in_warp = lane >> 2;           // rows r and r + 8 of this warp's 16
+  const int qrow0 = q0 + warp * 16 + row_in_warp;  // position in sequence of row r
+
+  for (int it = 0; it < n_kv; ++it) {
+    const int buf = it & 1;
+    cp_async_wait<0>();
+    __syncthreads();
+    if (it + 1 < n_kv) {
+      const int k0n = kv_lo + (it + 1) * ATT_BN;
+      load_tile_async<THREADS>(sK + (buf ^ 1) * ATT_BN * 128, kg + int64_t(k0n) * stride, stride,
+                               ATT_BN, kv_hi - k0n);
+      load_tile_async<THREADS>(sV + (buf ^ 1) * ATT_BN * 128, vg + int64_t(k0n) * stride, stride,
+                               ATT_BN, kv_hi - k0n);
+      cp_async_commit();
+    }
+    if (it == 0) {
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int c = kk * 2 + (lane >> 4);
+        ldsm_x4(sQ + tile_off(r, c), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+      }
+    }
+    const uint32_t kt = sK + buf * ATT_BN * 128;
+    const uint32_t vt = sV + buf * ATT_BN * 128;
+    const int k0 = kv_lo + it * ATT_BN;
+
+    // S = Q K^T for this warp's 16 rows x 64 keys
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {
+        const int mid = lane >> 3;
+        const int r = (jp * 2 + (mid >> 1)) * 8 + (lane & 7);
+        const int c = kk * 2 + (mid & 1);
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(kt + tile_off(r, c), b0, b1, b2, b3);
+        mma_bf16_16816(s[jp * 2], qf[kk], b0, b1);
+        mma_bf16_16816(s[jp * 2 + 1], qf[kk], b2, b3);
+      }
+    }
+
+    // scale into the exp2 domain and mask
+    const bool need_mask = (half_window >= 0) || (k0 + ATT_BN > kv_hi);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = s[j][e] * scale_log2;
+        if (need_mask) {
+          const int key = k0 + j * 8 + (lane & 3) * 2 + (e & 1);
+          const int qi = qrow0 + (e >> 1) * 8;
+          bool ok = key < kv_hi;
+          if (half_window >= 0) ok = ok && (abs(qi - key) <= half_window);
+          if (!ok) v = -INFINITY;
+        }
+        s[j][e] = v;
+      }
+    }
+    // online softmax for rows r (e = 0,1) and r + 8 (e = 2,3)
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fmaxf(s[j][h2 * 2], s[j][h2 * 2 + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[h2], mx);
+      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = fast_exp2(m_run[h2] - m_safe);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float p0 = fast_exp2(s[j][h2 * 2] - m_safe);
+        const float p1 = fast_exp2(s[j][h2 * 2 + 1] - m_safe);
+        s[j][h2 * 2] = p0;
+        s[j][h2 * 2 + 1] = p1;
+        sum += p0 + p1;
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l_run[h2] = l_run[h2] * alpha + sum;
+      m_run[h2] = m_new;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o_acc[j][h2 * 2] *= alpha;
+        o_acc[j][h2 * 2 + 1] *= alpha;
+      }
+    }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {
+        const int mid = lane >> 3;
+        const int r = kk * 16 + (mid & 1) * 8 + (lane & 7);
+        const int c = jp * 2 + (mid >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(vt + tile_off(r, c), b0, b1, b2, b3);
+        mma_bf16_16816(o_acc[jp * 2], pa, b0, b1);
+        mma_bf16_16816(o_acc[jp * 2 + 1], pa, b2, b3);
+      }
+    }
+  }
+
+  // normalise, stage this warp's 16 x 64 outputs in its own rows of the Q tile, store 16 B wide
+  const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
+  const float inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int r0 = warp * 16 + row_in_warp;
+    const uint32_t w0 = pack_bf16(o_acc[j][0] * inv0, o_acc[j][1] * inv0);
+    const uint32_t w1 = pack_bf16(o_acc[j][2] * inv1, o_acc[j][3] * inv1);
+    const uint32_t a0 = sQ + tile_off(r0, j) + (lane & 3) * 4;
+    const uint32_t a1 = sQ + tile_off(r0 + 8, j) + (lane & 3) * 4;
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(a0), "r"(w0) : "memory");
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(a1), "r"(w1) : "memory");
+  }
+  __syncwarp();
+  __nv_bfloat16* og = out + int64_t(seq_begin) * H + head * ATT_D;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = i * 32 + lane;
+    const int r = warp * 16 + (idx >> 3), c = idx & 7;
+    if (q0 + r < len) {
+      uint4 v;
+      asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                   : "r"(sQ + tile_off(r, c)));
+      *reinterpret_cast<uint4*>(og + int64_t(q0 + r) * H + c * 8) = v;
+    }
+  }
+}
+
+int attn_pick_bm(int max_seqlen) {
+  if (max_seqlen <= 16) return 16;
+  if (max_seqlen <= 32) return 32;
+  return 64;
+}
+
+int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int bm, int32_t* tile_start,
+                  cudaStream_t st) {
+  attn_schedule_kernel<<<1, 1024, 0, st>>>(cu_seqlens, n_seqs, bm, tile_start);
+  PE_LAUNCH_CHECK("attn_schedule_kernel");
+  return PE_OK;
+}
+
+int attn_run(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_start, int n_seqs,
+             int64_t T, int nh, int half_window, int bm, void* out, int32_t* status,
+             cudaStream_t st) {
+  (void)status;
+  // Upper bound on the number of query tiles given only the capacities.
+  const int64_t max_tiles = T / bm + n_seqs;
+  PE_REQUIRE(max_tiles < (1ll << 31), "attention: too many tiles");
+  dim3 grid((unsigned)max_tiles, (unsigned)nh);
+  const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(qkv);
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  switch (bm) {
+    case 16:
+      attn_varlen_mma_kernel<1><<<grid, 32, 0, st>>>(q, cu_seqlens, tile_start, n_seqs, nh, half_window, o);
+      break;
+    case 32:
+      attn_varlen_mma_kernel<2><<<grid, 64, 0, st>>>(q, cu_seqlens, tile_start, n_seqs, nh, half_window, o);
+      break;
+    case 64:
+      attn_varlen_mma_kernel<4><<<grid, 128, 0, st>>>(q, cu_seqlens, tile_start, n_seqs, nh, half_window, o);
+      break;
+    default:
+      set_last_error("attention: unsupported query tile %d", bm);
+      return PE_ERR_ARG;
+  }
+  PE_LAUNCH_CHECK("attn_varlen_mma_kernel");
+  return PE_OK;
+}
+
+}  // namespace pe
+
+extern "C" size_t pe_attn_workspace_bytes(int64_t T, int n_seqs) {
+  (void)T;
+  return (size_t(n_seqs) + 2) * sizeof(int32_t);
+}
+
+extern "C" int pe_attn_varlen(const void* qkv, const int32_t* cu_seqlens, int n_seqs, int64_t T,
+                              int nh, int half_window, int max_seqlen, void* out, void* workspace,
+                              size_t workspace_bytes, int32_t* status, void* stream) {
+  using namespace pe;
+  PE_REQUIRE(qkv && cu_seqlens && out && workspace, "pe_attn_varlen: null pointer");
+  PE_REQUIRE(n_seqs > 0 && T >= 0 && nh > 0 && nh <= 65535, "pe_attn_varlen: bad sizes");
+  PE_REQUIRE(max_seqlen > 0, "pe_attn_varlen: max_seqlen must be positive");
+  if (workspace_bytes < pe_attn_workspace_bytes(T, n_seqs)) {
+    set_last_error("pe_attn_varlen: workspace %zu < %zu bytes", workspace_bytes,
+                   pe_attn_workspace_bytes(T, n_seqs));
+    return PE_ERR_WORKSPACE;
+  }
+  if (T == 0) return PE_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int32_t* tile_start = static_cast<int32_t*>(workspace);
+  const int bm = attn_pick_bm(max_seqlen);
+  int rc = attn_schedule(cu_seqlens, n_seqs, bm, tile_start, st);
+  if (rc != PE_OK) return rc;
+  return attn_run(qkv, cu_seqlens, tile_start, n_seqs, T, nh, half_window, bm, out, status, st);
+}

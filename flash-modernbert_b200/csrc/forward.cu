@@ -1,0 +1,147 @@
+// The whole packed forward as one host call: embedding + LayerNorm, then per layer
+// add+LN -> Wqkv -> RoPE -> varlen attention -> Wo -> add+LN -> Wi(+GeGLU) -> Wo_mlp,
+// with the MLP residual deferred into the next layer's add+LN, and the final norm.
+// All launches go to the caller's stream; the caller owns every buffer.
+#include "pe_host.h"
+
+namespace pe {
+
+static int g_options[OPT_COUNT] = {0, /*OPT_FUSED_GEGLU*/ 1};
+
+int get_option(int key) { return (key > 0 && key < OPT_COUNT) ? g_options[key] : 0; }
+
+static size_t align_up(size_t v) { return (v + 255) & ~size_t(255); }
+
+struct Workspace {
+  size_t x, normed, qkv, ctx, tmp, act, proj, tiles, total;
+};
+
+static Workspace plan(const pe_model* m, int64_t T, int n_seqs) {
+  Workspace w;
+  const size_t H = (size_t)m->hidden, I = (size_t)m->intermediate;
+  const size_t rows = (size_t)(T > 0 ? T : 1);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t o = off;
+    off += align_up(bytes);
+    return o;
+  };
+  w.x = take(rows * H * 2);
+  w.normed = take(rows * H * 2);
+  w.qkv = take(rows * 3 * H * 2);
+  w.ctx = take(rows * H * 2);
+  w.tmp = take(rows * H * 2);
+  w.act = take(rows * I * 2);
+  w.proj = take(rows * 2 * I * 2);  // used only when the fused Wi+GeGLU kernel is switched off
+  w.tiles = take(pe_attn_workspace_bytes(T, n_seqs));
+  w.total = off;
+  return w;
+}
+
+static int check_model(const pe_model* m) {
+  PE_REQUIRE(m != nullptr, "model is NULL");
+  PE_REQUIRE(m->head_dim == 64, "head_dim=%d: only 64 is supported", m->head_dim);
+  PE_REQUIRE(m->hidden > 0 && m->hidden == m->n_heads * 64 && m->hidden <= 2048,
+             "hidden=%d must equal n_heads*64 and be <= 2048", m->hidden);
+  PE_REQUIRE(m->intermediate > 0 && m->intermediate % 8 == 0, "intermediate=%d must be a multiple of 8",
+             m->intermediate);
+  PE_REQUIRE(m->n_layers > 0 && m->layers != nullptr, "model has no layers");
+  PE_REQUIRE(m->tok_emb && m->emb_norm_w && m->final_norm_w && m->rope_global && m->rope_local,
+             "model has a NULL weight or RoPE table");
+  PE_REQUIRE(m->max_positions > 0 && m->vocab > 0, "bad max_positions/vocab");
+  for (int l = 0; l < m->n_layers; ++l) {
+    const pe_layer_weights& L = m->layers[l];
+    PE_REQUIRE(L.wqkv && L.wo && L.mlp_norm_w && L.wi && L.wo_mlp, "layer %d has a NULL weight", l);
+  }
+  return PE_OK;
+}
+
+}  // namespace pe
+
+extern "C" int pe_set_option(int key, int value) {
+  if (key <= 0 || key >= pe::OPT_COUNT) {
+    pe::set_last_error("pe_set_option: unknown key %d", key);
+    return PE_ERR_ARG;
+  }
+  pe::g_options[key] = value;
+  return PE_OK;
+}
+
+extern "C" size_t pe_forward_workspace_bytes(const pe_model* model, int64_t T, int n_seqs) {
+  if (model == nullptr || T < 0 || n_seqs < 0) return 0;
+  return pe::plan(model, T, n_seqs).total;
+}
+
+extern "C" int pe_forward_packed(const pe_model* model, const int64_t* ids,
+                                 const int32_t* cu_seqlens, const int64_t* position_ids, int64_t T,
+                                 int n_seqs, int max_seqlen, void* workspace, size_t workspace_bytes,
+                                 void* out, int32_t* status, void* stream) {
+  using namespace pe;
+  int rc = check_model(model);
+  if (rc != PE_OK) return rc;
+  PE_REQUIRE(ids && cu_seqlens && position_ids && workspace && out && status,
+             "pe_forward_packed: null pointer");
+  PE_REQUIRE(T >= 0 && n_seqs > 0 && max_seqlen > 0, "pe_forward_packed: bad sizes");
+  PE_REQUIRE(max_seqlen <= model->max_positions,
+             "pe_forward_packed: max_seqlen %d exceeds the RoPE table (%d rows)", max_seqlen,
+             model->max_positions);
+  const Workspace w = plan(model, T, n_seqs);
+  if (workspace_bytes < w.total) {
+    set_last_error("pe_forward_packed: workspace %zu < %zu bytes", workspace_bytes, w.total);
+    return PE_ERR_WORKSPACE;
+  }
+  if (T == 0) return PE_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  void* x = ws + w.x;
+  void* normed = ws + w.normed;
+  void* qkv = ws + w.qkv;
+  void* ctx = ws + w.ctx;
+  void* tmp = ws + w.tmp;
+  void* act = ws + w.act;
+  void* proj = ws + w.proj;
+  int32_t* tiles = reinterpret_cast<int32_t*>(ws + w.tiles);
+  const int H = model->hidden, I = model->intermediate, nh = model->n_heads;
+  const float eps = model->eps;
+
+#define PE_TRY(call)            \
+  do {                          \
+    rc = (call);                \
+    if (rc != PE_OK) return rc; \
+  } while (0)
+
+  PE_TRY(pe_embed_ln(ids, model->tok_emb, model->emb_norm_w, eps, T, H, model->vocab, x, status, st));
+  const int bm = attn_pick_bm(max_seqlen);
+  PE_TRY(attn_schedule(cu_seqlens, n_seqs, bm, tiles, st));
+
+  bool pending = false;  // tmp holds the previous layer's MLP output, not yet added to x
+  for (int l = 0; l < model->n_layers; ++l) {
+    const pe_layer_weights& L = model->layers[l];
+    const void* attn_in = normed;
+    if (L.attn_norm_w != nullptr) {
+      PE_TRY(pe_add_ln(x, pending ? tmp : nullptr, L.attn_norm_w, eps, T, H, pending ? x : nullptr,
+                       normed, st));
+    } else {
+      if (pending) PE_TRY(pe_add_ln(x, tmp, nullptr, eps, T, H, x, nullptr, st));
+      attn_in = x;
+    }
+    PE_TRY(pe_gemm_bf16_tn(attn_in, L.wqkv, qkv, T, 3 * H, H, status, st));
+    PE_TRY(pe_rope_qk_inplace(qkv, position_ids, L.is_global ? model->rope_global : model->rope_local,
+                              model->max_positions, T, nh, status, st));
+    PE_TRY(attn_run(qkv, cu_seqlens, tiles, n_seqs, T, nh, L.is_global ? -1 : model->half_window, bm,
+                    ctx, status, st));
+    PE_TRY(pe_gemm_bf16_tn(ctx, L.wo, tmp, T, H, H, status, st));
+    PE_TRY(pe_add_ln(x, tmp, L.mlp_norm_w, eps, T, H, x, normed, st));
+    if (get_option(OPT_FUSED_GEGLU)) {
+      PE_TRY(pe_gemm_geglu_bf16(normed, L.wi, act, T, I, H, status, st));
+    } else {
+      PE_TRY(pe_gemm_bf16_tn(normed, L.wi, proj, T, 2 * I, H, status, st));
+      PE_TRY(pe_geglu(proj, T, I, act, st));
+    }
+    PE_TRY(pe_gemm_bf16_tn(act, L.wo_mlp, tmp, T, H, I, status, st));
+    pending = true;
+  }
+  PE_TRY(pe_add_ln(x, pending ? tmp : nullptr, model->final_norm_w, eps, T, H, nullptr, out, st));
+#undef PE_TRY
+  return PE_OK;
+}

@@ -1,0 +1,285 @@
+// bf16 "TN" GEMM for the four ModernBERT projections, C[M, N] = A[M, K] * W[N, K]^T,
+// written for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with the
+// fp32 accumulator in tensor memory, persistent CTAs.
+//
+// One CTA per SM walks output tiles of 128 rows x 256 accumulator columns.
+//   warp 0      : TMA producer (one elected lane) - A box 128x64, two W boxes 128x64
+//   warp 1      : allocates tensor memory, issues tcgen05.mma (one elected lane)
+//   warps 2..5  : epilogue - tcgen05.ld the accumulator, round to bf16, store
+// Tensor memory holds two 256-column accumulators, so the epilogue of tile i
+// overlaps the main loop of tile i+1.  The k loop runs over 64-wide blocks through
+// a 4-stage ring of (A 16 KB + W 32 KB) buffers guarded by full/empty mbarriers.
+//
+// GEGLU mode computes the first half of the MLP in one pass: the 256 accumulator
+// columns of a tile are 128 columns of the gelu input (rows n0.. of Wi) and the
+// matching 128 gate columns (rows I + n0.. of Wi); the epilogue rounds both to
+// bf16, as the unfused path materialises them, and writes gelu(a) * gate.
+//
+// Every mbarrier wait is bounded; a wait that gives up records a code in the
+// status word and the CTA unwinds through the common exit, which frees its
+// tensor memory.
+#include "pe_host.h"
+#include "pe_ptx.cuh"
+
+namespace pe {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t TMEM_COLS = 512;
+
+__device__ __forceinline__ float gelu_erf(float a) {
+  return a * 0.5f * (1.0f + erff(a * 0.70710678118654752440f));
+}
+__device__ __forceinline__ float round_bf16(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+template <bool GEGLU>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    __nv_bfloat16* __restrict__ C, int M, int n_out, int K, int gate_row0,
+                    int num_m, int num_n, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = base + STAGES * STAGE_BYTES;
+  // barrier slots (8 bytes each): full[0..3], empty[4..7], tmem_full[8..9], tmem_empty[10..11]
+  auto bar = [&](int i) { return bar_base + 8u * i; };
+  const uint32_t tmem_slot = bar_base + 8u * 12;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (K + BK - 1) / BK;
+  const int num_tiles = num_m * num_n;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(bar(i), 1);
+      mbar_init(bar(4 + i), 1);
+    }
+    mbar_init(bar(8), 1);
+    mbar_init(bar(9), 1);
+    mbar_init(bar(10), 4);
+    mbar_init(bar(11), 4);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    if (elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / num_n) * BM;
+        const int nt = tile % num_n;
+        const int brow0 = GEGLU ? nt * 128 : nt * BN;
+        const int brow1 = GEGLU ? gate_row0 + nt * 128 : nt * BN + 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar(4 + stage), phase ^ 1u, status, ST_GEMM_PRODUCER_TIMEOUT)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          mbar_expect_tx(bar(stage), STAGE_BYTES);
+          tma_load_2d(sa, &tmA, bar(stage), kb * BK, m0);
+          tma_load_2d(sb, &tmB, bar(stage), kb * BK, brow0);
+          tma_load_2d(sb + B_BYTES / 2, &tmB, bar(stage), kb * BK, brow1);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(bar(10 + acc), acc_phase ^ 1u, status, ST_GEMM_MMA_TIMEOUT)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar(stage), phase, status, ST_GEMM_MMA_TIMEOUT)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = base + stage * STAGE_BYTES;
+          const uint64_t adesc = umma_smem_desc_sw128(sa, 1024);
+          const uint64_t bdesc = umma_smem_desc_sw128(sa + A_BYTES, 1024);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            // 16 bf16 along K = 32 bytes = 2 descriptor address units inside the swizzle atom
+            umma_ss(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(bar(4 + stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(bar(8 + acc));
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    uint32_t acc = 0, acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m0 = (tile / num_n) * BM;
+      const int nt = tile % num_n;
+      if (!mbar_wait(bar(8 + acc), acc_phase, status, ST_GEMM_EPILOGUE_TIMEOUT)) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      if constexpr (!GEGLU) {
+        const int col0 = nt * BN;
+        __nv_bfloat16* crow = C + size_t(row) * n_out + col0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_addr + c * 32, v);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int col = col0 + c * 32 + j * 8;
+              if (col + 8 <= n_out) {
+                uint4 o;
+                o.x = pack_bf16(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
+                o.y = pack_bf16(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
+                o.z = pack_bf16(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
+                o.w = pack_bf16(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
+                *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) = o;
+              }
+            }
+          }
+        }
+      } else {
+        const int col0 = nt * 128;
+        __nv_bfloat16* crow = C + size_t(row) * n_out + col0;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t va[32], vg[32];
+          tmem_ld_32x32(t_addr + c * 32, va);
+          tmem_ld_32x32(t_addr + 128 + c * 32, vg);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int col = col0 + c * 32 + j * 8;
+              if (col + 8 <= n_out) {
+                float r[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const float a = round_bf16(__uint_as_float(va[j * 8 + e]));
+                  const float g = round_bf16(__uint_as_float(vg[j * 8 + e]));
+                  r[e] = gelu_erf(a) * g;
+                }
+                uint4 o;
+                o.x = pack_bf16(r[0], r[1]);
+                o.y = pack_bf16(r[2], r[3]);
+                o.z = pack_bf16(r[4], r[5]);
+                o.w = pack_bf16(r[6], r[7]);
+                *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(10 + acc));
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // Common exit: every role arrives here (each of its waits is bounded).
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool GEGLU>
+static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_out, int K,
+                       int w_rows, int gate_row0, int32_t* status, cudaStream_t stream) {
+  static bool attr_set[2] = {false, false};
+  auto kern = gemm_bf16_tn_kernel<GEGLU>;
+  if (!attr_set[GEGLU ? 1 : 0]) {
+    PE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
+    attr_set[GEGLU ? 1 : 0] = true;
+  }
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM);
+  if (rc != PE_OK) return rc;
+  rc = make_tmap_bf16_2d(&tmB, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)K, 128);
+  if (rc != PE_OK) return rc;
+  const int num_m = int((M + BM - 1) / BM);
+  const int cols_per_tile = GEGLU ? 128 : BN;
+  const int num_n = (n_out + cols_per_tile - 1) / cols_per_tile;
+  const long long tiles = (long long)num_m * num_n;
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, static_cast<__nv_bfloat16*>(C),
+                                                  (int)M, n_out, K, gate_row0, num_m, num_n,
+                                                  status);
+  PE_LAUNCH_CHECK("gemm_bf16_tn_kernel");
+  return PE_OK;
+}
+
+static int check_gemm_args(const void* A, const void* W, const void* C, int64_t M, int n, int K,
+                           const char* who) {
+  PE_REQUIRE(A && W && C, "%s: null pointer", who);
+  PE_REQUIRE(M >= 0 && M < (1ll << 31) - 256, "%s: M=%lld out of range", who, (long long)M);
+  PE_REQUIRE(n > 0 && n % 8 == 0, "%s: output columns %d must be a positive multiple of 8", who, n);
+  PE_REQUIRE(K > 0 && K % 8 == 0, "%s: K=%d must be a positive multiple of 8", who, K);
+  PE_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)C & 15) == 0,
+             "%s: pointers must be 16-byte aligned", who);
+  return PE_OK;
+}
+
+}  // namespace pe
+
+extern "C" int pe_gemm_bf16_tn(const void* A, const void* W, void* C, int64_t M, int Nout, int K,
+                               int32_t* status, void* stream) {
+  int rc = pe::check_gemm_args(A, W, C, M, Nout, K, "pe_gemm_bf16_tn");
+  if (rc != PE_OK) return rc;
+  if (M == 0) return PE_OK;
+  return pe::launch_gemm<false>(A, W, C, M, Nout, K, Nout, 0, status,
+                                static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int pe_gemm_geglu_bf16(const void* A, const void* Wi, void* out, int64_t M, int I, int K,
+                                  int32_t* status, void* stream) {
+  int rc = pe::check_gemm_args(A, Wi, out, M, I, K, "pe_gemm_geglu_bf16");
+  if (rc != PE_OK) return rc;
+  if (M == 0) return PE_OK;
+  return pe::launch_gemm<true>(A, Wi, out, M, I, K, 2 * I, I, status,
+                               static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,55 @@
+// Host-side helpers shared by the translation units of libpe_b200.so: error
+// recording for the C ABI, launch checks, and TMA descriptor construction.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/pe_b200.h"
+
+namespace pe {
+
+void set_last_error(const char* fmt, ...);
+
+// Returns PE_OK or records the CUDA error text and returns PE_ERR_CUDA.
+int check_cuda(cudaError_t e, const char* what);
+
+#define PE_CUDA(call)                                  \
+  do {                                                 \
+    int _rc = ::pe::check_cuda((call), #call);         \
+    if (_rc != PE_OK) return _rc;                      \
+  } while (0)
+
+#define PE_LAUNCH_CHECK(name) PE_CUDA(cudaGetLastError())
+
+#define PE_REQUIRE(cond, ...)                          \
+  do {                                                 \
+    if (!(cond)) {                                     \
+      ::pe::set_last_error(__VA_ARGS__);               \
+      return PE_ERR_ARG;                               \
+    }                                                  \
+  } while (0)
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// Encodes a 2-D bf16 tensor map: global tensor [rows, cols] with `row_stride_elts`
+// between rows, box [box_rows, 64 columns], 128-byte swizzle, zero fill outside.
+int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                      uint64_t row_stride_elts, uint32_t box_rows);
+
+// Attention in two steps so that a forward builds the query-tile table once and
+// reuses it for every layer (attn_varlen.cu).
+int attn_pick_bm(int max_seqlen);
+int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int bm, int32_t* tile_start,
+                  cudaStream_t st);
+int attn_run(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_start, int n_seqs,
+             int64_t T, int nh, int half_window, int bm, void* out, int32_t* status,
+             cudaStream_t st);
+
+// Process-wide switches (pe_set_option).
+enum Option : int { OPT_FUSED_GEGLU = 1, OPT_COUNT };
+int get_option(int key);
+
+}  // namespace pe
