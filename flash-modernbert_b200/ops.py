@@ -1,0 +1,183 @@
+"""Single-op entry points on torch tensors, one C-ABI call each.
+
+Names and argument meaning follow the inference branches of packed_encoders/ops.py
+(`fused_layer_norm` 191-208, `fused_add_layer_norm` 303-314, `_linear` 290-300,
+`fused_geglu` 275-280, `geglu_mlp` 317-319, `flash_attention_qkv_bshd` 485-532), so
+the parity tests read like the reference's. `packed_forward` does not go through
+these wrappers (it is one C call); they exist for callers that compose their own
+pipeline and for per-kernel tests. All tensors must be CUDA bf16 and contiguous.
+"""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from .errors import PackedEncodersError
+
+
+def _bf16_cuda(t: Tensor, name: str) -> Tensor:
+    if not t.is_cuda or t.dtype != torch.bfloat16:
+        raise PackedEncodersError(f"{name} must be a CUDA bf16 tensor, got {t.dtype} on {t.device}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+class _Call:
+    """Device guard + stream + status word for one library call."""
+
+    def __init__(self, ref: Tensor):
+        self.lib = _lib.load()
+        self.device = ref.device
+        self.guard = torch.cuda.device(self.device)
+
+    def __enter__(self):
+        self.guard.__enter__()
+        self.stream = _lib.current_stream_ptr()
+        return self
+
+    def __exit__(self, *exc):
+        return self.guard.__exit__(*exc)
+
+
+_status_words: dict[int, Tensor] = {}
+
+
+def status_word(device: torch.device) -> Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status_words:
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _status_words[idx]
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronise and raise if any kernel launched through this module reported a fault."""
+    word = status_word(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise _lib.NativeLibraryError(f"a CUDA kernel reported status {code}")
+
+
+def fused_layer_norm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
+    x = _bf16_cuda(x, "x")
+    flat = x.reshape(-1, x.shape[-1])
+    y = torch.empty_like(flat)
+    with _Call(x) as c:
+        _lib.check(c.lib.pe_add_ln(flat.data_ptr(), None, _bf16_cuda(weight, "weight").data_ptr(),
+                                   float(eps), flat.shape[0], flat.shape[1], None, y.data_ptr(),
+                                   c.stream), "pe_add_ln")
+    return y.view(x.shape)
+
+
+def fused_add_layer_norm(x: Tensor, residual: Tensor, weight: Tensor, eps: float) -> tuple[Tensor, Tensor]:
+    """`x_new = x + residual` (rounded to bf16), `y = LN(x_new)`; returns `(x_new, y)`."""
+    x = _bf16_cuda(x, "x")
+    residual = _bf16_cuda(residual, "residual")
+    flat = x.reshape(-1, x.shape[-1])
+    x_new = torch.empty_like(flat)
+    y = torch.empty_like(flat)
+    with _Call(x) as c:
+        _lib.check(c.lib.pe_add_ln(flat.data_ptr(), residual.reshape(flat.shape).data_ptr(),
+                                   _bf16_cuda(weight, "weight").data_ptr(), float(eps),
+                                   flat.shape[0], flat.shape[1], x_new.data_ptr(), y.data_ptr(),
+                                   c.stream), "pe_add_ln")
+    return x_new.view(x.shape), y.view(x.shape)
+
+
+def embed_layer_norm(ids: Tensor, table: Tensor, weight: Tensor, eps: float) -> Tensor:
+    """`LN(table[ids])`: the embedding prologue of packed_encoders/forward.py:472-476."""
+    table = _bf16_cuda(table, "table")
+    ids = ids.contiguous()
+    out = torch.empty(ids.numel(), table.shape[1], dtype=torch.bfloat16, device=table.device)
+    with _Call(table) as c:
+        _lib.check(c.lib.pe_embed_ln(ids.data_ptr(), table.data_ptr(),
+                                     _bf16_cuda(weight, "weight").data_ptr(), float(eps),
+                                     ids.numel(), table.shape[1], table.shape[0], out.data_ptr(),
+                                     status_word(table.device).data_ptr(), c.stream), "pe_embed_ln")
+    return out.view(*ids.shape, table.shape[1])
+
+
+def _linear(x: Tensor, weight: Tensor) -> Tensor:
+    """`x @ weight.T`, weight `[out, in]` as `nn.Linear` stores it; no bias."""
+    x = _bf16_cuda(x, "x")
+    weight = _bf16_cuda(weight, "weight")
+    flat = x.reshape(-1, x.shape[-1])
+    out = torch.empty(flat.shape[0], weight.shape[0], dtype=torch.bfloat16, device=x.device)
+    with _Call(x) as c:
+        _lib.check(c.lib.pe_gemm_bf16_tn(flat.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                                         flat.shape[0], weight.shape[0], weight.shape[1],
+                                         status_word(x.device).data_ptr(), c.stream),
+                   "pe_gemm_bf16_tn")
+    return out.view(*x.shape[:-1], weight.shape[0])
+
+
+def fused_geglu(proj: Tensor) -> Tensor:
+    proj = _bf16_cuda(proj, "proj")
+    flat = proj.reshape(-1, proj.shape[-1])
+    inter = flat.shape[1] // 2
+    out = torch.empty(flat.shape[0], inter, dtype=torch.bfloat16, device=proj.device)
+    with _Call(proj) as c:
+        _lib.check(c.lib.pe_geglu(flat.data_ptr(), flat.shape[0], inter, out.data_ptr(), c.stream),
+                   "pe_geglu")
+    return out.view(*proj.shape[:-1], inter)
+
+
+def linear_geglu(x: Tensor, wi: Tensor) -> Tensor:
+    """`fused_geglu(_linear(x, wi))` as one kernel (the projection never reaches memory)."""
+    x = _bf16_cuda(x, "x")
+    wi = _bf16_cuda(wi, "wi")
+    flat = x.reshape(-1, x.shape[-1])
+    inter = wi.shape[0] // 2
+    out = torch.empty(flat.shape[0], inter, dtype=torch.bfloat16, device=x.device)
+    with _Call(x) as c:
+        _lib.check(c.lib.pe_gemm_geglu_bf16(flat.data_ptr(), wi.data_ptr(), out.data_ptr(),
+                                            flat.shape[0], inter, wi.shape[1],
+                                            status_word(x.device).data_ptr(), c.stream),
+                   "pe_gemm_geglu_bf16")
+    return out.view(*x.shape[:-1], inter)
+
+
+def geglu_mlp(x: Tensor, wi: Tensor, wo: Tensor) -> Tensor:
+    return _linear(linear_geglu(x, wi), wo)
+
+
+def rope_table(theta: float, max_positions: int, device) -> Tensor:
+    """bf16 `[max_positions, 64]`: cos of the 32 frequencies, then sin."""
+    table = torch.empty(max_positions, 64, dtype=torch.bfloat16, device=device)
+    with _Call(table) as c:
+        _lib.check(c.lib.pe_rope_table(float(theta), max_positions, table.data_ptr(), c.stream),
+                   "pe_rope_table")
+    return table
+
+
+def rope_qk_inplace(qkv: Tensor, position_ids: Tensor, table: Tensor, n_heads: int) -> Tensor:
+    """Rotate the q and k thirds of the fused `qkv [T, 3*n_heads*64]` in place."""
+    if not qkv.is_contiguous():
+        raise PackedEncodersError("qkv must be contiguous for the in-place rotation")
+    qkv = _bf16_cuda(qkv, "qkv")
+    with _Call(qkv) as c:
+        _lib.check(c.lib.pe_rope_qk_inplace(qkv.data_ptr(), position_ids.contiguous().data_ptr(),
+                                            _bf16_cuda(table, "table").data_ptr(), table.shape[0],
+                                            qkv.shape[0], n_heads,
+                                            status_word(qkv.device).data_ptr(), c.stream),
+                   "pe_rope_qk_inplace")
+    return qkv
+
+
+def attention_varlen_qkv(qkv: Tensor, cu_seqlens: Tensor, max_seqlen: int, n_heads: int,
+                         half_window: int | None) -> Tensor:
+    """Varlen attention on the fused, already-rotated `qkv [T, 3*n_heads*64]`;
+    `half_window=None` is full attention. Returns `[T, n_heads*64]`."""
+    qkv = _bf16_cuda(qkv, "qkv")
+    total = qkv.shape[0]
+    n_seqs = cu_seqlens.numel() - 1
+    out = torch.empty(total, n_heads * 64, dtype=torch.bfloat16, device=qkv.device)
+    with _Call(qkv) as c:
+        ws_bytes = int(c.lib.pe_attn_workspace_bytes(total, n_seqs))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=qkv.device)
+        _lib.check(c.lib.pe_attn_varlen(qkv.data_ptr(), cu_seqlens.contiguous().data_ptr(), n_seqs,
+                                        total, n_heads, -1 if half_window is None else half_window,
+                                        int(max_seqlen), out.data_ptr(), ws.data_ptr(), ws_bytes,
+                                        status_word(qkv.device).data_ptr(), c.stream),
+                   "pe_attn_varlen")
+    return out

@@ -1,0 +1,120 @@
+"""Varlen attention against the fp32 per-sequence reference (the oracle restates
+tests/test_packed_short_attention.py:33-46 of the reference), through the C ABI."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import packed_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+EDGE_LENGTHS = [1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 191, 192, 193, 257, 700]
+
+
+def _qkv(lengths, n_heads, device, seed=0, scale=1.0):
+    gen = torch.Generator().manual_seed(seed)
+    total = sum(lengths)
+    qkv = torch.randn(total, 3, n_heads, 64, generator=gen)
+    qkv[:, 0] *= scale
+    qkv = qkv.to(torch.bfloat16)
+    cu = torch.zeros(len(lengths) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lengths).cumsum(0)
+    return qkv, cu
+
+
+def _run(qkv, cu, n_heads, half_window, device, max_seqlen=None):
+    from flash_modernbert_b200 import ops
+
+    lengths = (cu[1:] - cu[:-1]).tolist()
+    flat = qkv.reshape(qkv.shape[0], -1).to(device)
+    return ops.attention_varlen_qkv(flat, cu.to(device), max_seqlen or max(lengths), n_heads, half_window)
+
+
+def _check(out, qkv, cu, half_window, what):
+    ref = O.attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu, half_window, faithful=False)
+    got = out.cpu().float().view_as(ref)
+    err = (got - ref).abs()
+    rep = O.cosine_report(got.reshape(got.shape[0], -1), ref.reshape(ref.shape[0], -1))
+    assert float(err.max()) < 0.03 and float(err.mean()) < 2e-3, (what, float(err.max()), float(err.mean()))
+    assert rep["min_token_cos"] > 0.9995, (what, rep)
+
+
+@pytest.mark.parametrize("half_window", [None, 64])
+def test_ragged_and_tile_edges(pe, cuda_device, half_window):
+    qkv, cu = _qkv(EDGE_LENGTHS, 12, cuda_device)
+    out = _run(qkv, cu, 12, half_window, cuda_device)
+    _check(out, qkv, cu, half_window, f"edges window={half_window}")
+
+
+@pytest.mark.parametrize("lengths", [[5], [16, 3, 16, 1], [32, 20, 7, 32], [48, 8, 30, 41, 19]])
+@pytest.mark.parametrize("half_window", [None, 64])
+def test_short_query_tiles(pe, cuda_device, lengths, half_window):
+    """max_seqlen <= 16 / <= 32 / <= 64 select the 16-, 32- and 64-row query tiles."""
+    qkv, cu = _qkv(lengths, 4, cuda_device, seed=1)
+    out = _run(qkv, cu, 4, half_window, cuda_device)
+    _check(out, qkv, cu, half_window, f"short {lengths}")
+
+
+def test_small_window_and_long_sequence(pe, cuda_device):
+    qkv, cu = _qkv([2048, 5, 900], 2, cuda_device, seed=2)
+    for hw in (None, 64, 8):
+        _check(_run(qkv, cu, 2, hw, cuda_device), qkv, cu, hw, f"long window={hw}")
+
+
+@pytest.mark.parametrize("scale", [0.01, 1.0, 8.0])
+def test_deterministic_and_finite(pe, cuda_device, scale):
+    # tests/test_packed_short_attention.py:95-107 of the reference
+    qkv, cu = _qkv([100, 37, 128], 12, cuda_device, seed=3, scale=scale)
+    a = _run(qkv, cu, 12, 64, cuda_device)
+    b = _run(qkv, cu, 12, 64, cuda_device)
+    assert torch.equal(a, b) and bool(torch.isfinite(a.float()).all())
+
+
+@pytest.mark.parametrize("half_window", [None, 64])
+def test_no_cross_sequence_leakage(pe, cuda_device, half_window):
+    # tests/test_packed_short_attention.py:110-124 of the reference
+    qkv, cu = _qkv([70, 45, 130], 12, cuda_device, seed=4)
+    base = _run(qkv, cu, 12, half_window, cuda_device)
+    other = qkv.clone()
+    other[70:, 1:] *= 100                                   # K and V of the other sequences
+    out = _run(other, cu, 12, half_window, cuda_device)
+    assert torch.equal(out[:70], base[:70])
+
+
+def test_trailing_empty_sequences_and_padding_tokens(pe, cuda_device):
+    """Graph buckets: cu_seqlens padded with repeats of T, tokens beyond cu[-1] ignored."""
+    qkv, cu = _qkv([40, 25], 4, cuda_device, seed=5)
+    base = _run(qkv, cu, 4, None, cuda_device)
+    padded_qkv = torch.cat([qkv, torch.randn(63, 3, 4, 64).to(torch.bfloat16)])
+    padded_cu = torch.cat([cu, torch.full((5,), 65, dtype=torch.int32)])
+    out = _run(padded_qkv, padded_cu, 4, None, cuda_device, max_seqlen=64)
+    assert torch.equal(out[:65], base)
+
+
+def test_full_size_properties(pe, cuda_device):
+    """cfg3 lengths (306,851 tokens, longest 8192), 12 heads: spot-check sequences against
+    the reference and check that uniform V gives V back (softmax rows sum to one)."""
+    from oracle import synthetic as S
+
+    lengths = S.workload("cfg3").sorted_by_length().lengths
+    total = sum(lengths)
+    gen = torch.Generator(device=cuda_device).manual_seed(0)
+    qkv = torch.randn(total, 3, 12, 64, device=cuda_device, generator=gen).to(torch.bfloat16)
+    cu = torch.zeros(len(lengths) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lengths).cumsum(0)
+    from flash_modernbert_b200 import ops
+
+    for hw in (None, 64):
+        out = ops.attention_varlen_qkv(qkv.view(total, -1), cu.to(cuda_device), max(lengths), 12, hw)
+        for n in (3, 17, 300, len(lengths) - 1):           # long, mid, short, shortest
+            s, e = int(cu[n]), int(cu[n + 1])
+            sub = qkv[s:e, :, 4:7].cpu()                    # three of the twelve heads
+            ref = O.attention(sub[:, 0], sub[:, 1], sub[:, 2], [0, e - s], hw, faithful=False)
+            got = out[s:e].view(e - s, 12, 64)[:, 4:7].cpu().float()
+            err = (got - ref).abs()
+            assert float(err.max()) < 0.03, (hw, n, float(err.max()))
+    const_v = qkv.clone()
+    const_v[:, 2] = 0.5
+    out = ops.attention_varlen_qkv(const_v.view(total, -1), cu.to(cuda_device), max(lengths), 12, 64)
+    assert float((out.float() - 0.5).abs().max()) < 4e-3

@@ -1,0 +1,262 @@
+"""End-to-end parity of the packed forward and of the pack()/unpack() API on a B200:
+against the CPU oracle, the Hugging Face eager golden, HF eager fp32 run on the host, and
+(when its install is present) the reference's own GPU packed_forward."""
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT
+from oracle import packed_oracle as O
+from oracle import synthetic as S
+
+pytestmark = pytest.mark.gpu
+
+COS_GATE = 0.999  # per-token cosine floor stated by the task's north star
+
+
+def _packed_inputs(wl, device):
+    cu = torch.zeros(len(wl.lengths) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(wl.lengths).cumsum(0)
+    pos = torch.cat([torch.arange(n) for n in wl.lengths])
+    return wl.ids.to(device), cu.to(device), wl.max_seqlen, pos.to(device)
+
+
+@pytest.fixture(scope="module")
+def tiny_models(cuda_device, golden_dir):
+    g = np.load(golden_dir / "hf_tiny.npz")
+    vocab = int(g["vocab"])
+    cpu = S.make_model("tiny", vocab)
+    gpu = S.make_model("tiny", vocab, dtype=torch.bfloat16, device=cuda_device)
+    return g, cpu, gpu, vocab
+
+
+def test_tiny_model_against_golden_and_oracle(pe, cuda_device, tiny_models):
+    from flash_modernbert_b200 import forward
+
+    g, cpu, gpu, vocab = tiny_models
+    wl = S.workload("tiny_mixed", vocab)
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    ids, cu, max_s, pos = _packed_inputs(wl, cuda_device)
+    out = pe.packed_forward(gpu, params, ids, cu, max_s, pos)
+    forward.get_binding(gpu, params).check(sync=True)
+    assert out.shape == (wl.total_tokens, 256) and out.dtype == torch.bfloat16
+    golden = torch.from_numpy(g["last_hidden_state"].astype(np.float32))
+    rep = O.cosine_report(out.cpu(), golden)
+    assert rep["min_token_cos"] >= COS_GATE and rep["max_abs"] < 0.25, rep
+    oracle = O.packed_forward(cpu, wl.ids, cu.cpu(), max_s, pos.cpu(), faithful=True)
+    rep_o = O.cosine_report(out.cpu(), oracle)
+    assert rep_o["min_token_cos"] >= 0.9995 and rep_o["max_abs"] < 0.13, rep_o
+    # position_ids=None means arange per sequence
+    assert torch.equal(pe.packed_forward(gpu, params, ids, cu, max_s, None), out)
+    # deterministic
+    assert torch.equal(pe.packed_forward(gpu, params, ids, cu, max_s, pos), out)
+
+
+def test_fused_and_unfused_mlp_agree(pe, cuda_device, tiny_models):
+    from flash_modernbert_b200 import _lib
+
+    _, _, gpu, vocab = tiny_models
+    wl = S.workload("tiny_short", vocab)
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    args = _packed_inputs(wl, cuda_device)
+    lib = _lib.load()
+    try:
+        fused = pe.packed_forward(gpu, params, *args)
+        _lib.check(lib.pe_set_option(_lib.OPT_FUSED_GEGLU, 0), "pe_set_option")
+        unfused = pe.packed_forward(gpu, params, *args)
+    finally:
+        lib.pe_set_option(_lib.OPT_FUSED_GEGLU, 1)
+    assert torch.equal(fused, unfused)
+
+
+def test_pack_unpack_api(pe, cuda_device, tiny_models):
+    from transformers.modeling_outputs import BaseModelOutput
+
+    _, cpu, gpu, vocab = tiny_models
+    wl = S.workload("tiny_short", vocab)
+    b, s = len(wl.lengths), wl.max_seqlen
+    ids = torch.zeros(b, s, dtype=torch.int64)
+    mask = torch.zeros(b, s, dtype=torch.int64)
+    for i, seq in enumerate(wl.sequences()):
+        ids[i, : seq.numel()] = seq
+        mask[i, : seq.numel()] = 1
+    stock = O.hf_eager_padded(cpu, ids, mask)
+    original = gpu.forward
+    report = pe.validate(gpu, seq_lens=(128, 512))
+    assert report.capability == (10, 0) and min(report.cosine.values()) >= 0.997
+    assert pe.pack(gpu, validate=False) is gpu
+    assert pe.pack(gpu) is gpu                                         # idempotent
+    try:
+        with torch.no_grad():
+            out = gpu(input_ids=ids.to(cuda_device), attention_mask=mask.to(cuda_device))
+        assert isinstance(out, BaseModelOutput)
+        hidden = out.last_hidden_state
+        assert hidden.shape == (b, s, 256)
+        real = mask.bool()
+        assert not bool(hidden.cpu()[~real].ne(0).any())               # pad rows exactly zero
+        rep = O.cosine_report(hidden.cpu()[real], stock[real])
+        assert rep["min_token_cos"] >= COS_GATE, rep
+        tup = gpu(input_ids=ids.to(cuda_device), attention_mask=mask.to(cuda_device), return_dict=False)
+        assert isinstance(tup, tuple) and torch.equal(tup[0], hidden)
+        nomask = gpu(input_ids=ids[:3, :8].to(cuda_device)).last_hidden_state
+        assert nomask.shape == (3, 8, 256)
+        for kw in ({"inputs_embeds": torch.zeros(1)}, {"output_attentions": True},
+                   {"output_hidden_states": True}, {"token_type_ids": torch.ones(1, 1)}):
+            with pytest.raises(NotImplementedError):
+                gpu(input_ids=ids.to(cuda_device), **kw)
+        with pytest.raises(NotImplementedError):
+            gpu(attention_mask=mask.to(cuda_device))
+        assert pe.get_state(gpu).params.hidden_size == 256
+    finally:
+        pe.unpack(gpu)
+    assert gpu.forward == original and not hasattr(gpu, "_packed_encoders")
+
+
+def test_bucketed_cuda_graphs(pe, cuda_device, tiny_models):
+    from flash_modernbert_b200 import forward
+
+    _, _, gpu, vocab = tiny_models
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    pe.pack(gpu, validate=False, cuda_graph=pe.GraphConfig(pad_to=256, max_batch=64, max_seq=64))
+    try:
+        runner = pe.get_state(gpu).packed_graph_runner
+        gen = torch.Generator().manual_seed(7)
+        for trial in range(6):
+            n = int(torch.randint(20, 64, (1,), generator=gen))
+            lengths = torch.randint(33, 49, (n,), generator=gen).tolist()
+            seqs = [torch.randint(5, vocab, (l,), generator=gen) for l in lengths]
+            batch = pe.pack_sequences(seqs, device=cuda_device)
+            graphed = pe.packed_forward(gpu, params, *batch.forward_args())
+            with pe.no_cuda_graph(gpu):
+                eager = pe.packed_forward(gpu, params, *batch.forward_args())
+            forward.get_binding(gpu, params).check(sync=True)
+            assert graphed.shape == eager.shape
+            assert torch.equal(graphed, eager), trial         # same kernels, same data => same bits
+        assert runner.replays == 6
+        # ragged traffic shares graphs: keys hold capacities only
+        assert runner.captures <= 5 and all(k[1] == 64 and k[2] == 64 for k in runner._cache)
+        long_batch = pe.pack_sequences([torch.randint(5, vocab, (100,), generator=gen)], device=cuda_device)
+        before = runner.eager_calls
+        pe.packed_forward(gpu, params, *long_batch.forward_args())    # over max_seq: eager
+        assert runner.eager_calls == before + 1
+        os.environ["PACKED_ENCODERS_GRAPH"] = "0"
+        try:
+            replays = runner.replays
+            pe.packed_forward(gpu, params, *batch.forward_args())
+            assert runner.replays == replays                          # kill switch
+        finally:
+            del os.environ["PACKED_ENCODERS_GRAPH"]
+        pe.set_cuda_graph(gpu, False)
+        assert not pe.get_state(gpu).graph_enabled
+    finally:
+        pe.unpack(gpu)
+
+
+@pytest.fixture(scope="module")
+def base_models(cuda_device):
+    cpu = S.make_model("base")
+    gpu = S.make_model("base", dtype=torch.bfloat16, device=cuda_device)
+    return cpu, gpu
+
+
+def test_base_cfg1_against_hf_eager(pe, cuda_device, base_models):
+    """cfg1 (32 sequences, 8,552 tokens) on ModernBERT-base: whole batch on the GPU, HF eager
+    fp32 on the host for a seeded subset of sequences (bounded CPU time)."""
+    from flash_modernbert_b200 import forward
+
+    cpu, gpu = base_models
+    wl = S.workload("cfg1")
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    ids, cu, max_s, pos = _packed_inputs(wl, cuda_device)
+    out = pe.packed_forward(gpu, params, ids, cu, max_s, pos)
+    forward.get_binding(gpu, params).check(sync=True)
+    assert bool(torch.isfinite(out.float()).all())
+    seqs = wl.sequences()
+    picks = [0, 7, 19, 31]
+    worst = 1.0
+    max_abs = 0.0
+    for n in picks:
+        ref = O.hf_eager_packed(cpu, [seqs[n]])
+        s, e = int(cu[n]), int(cu[n + 1])
+        rep = O.cosine_report(out[s:e].cpu(), ref)
+        worst = min(worst, rep["min_token_cos"])
+        max_abs = max(max_abs, rep["max_abs"])
+    print(f"cfg1 vs HF eager fp32: min per-token cosine {worst:.6f}, max-abs {max_abs:.4f}")
+    assert worst >= COS_GATE, (worst, max_abs)
+
+
+def test_base_padded_api_matches_packed(pe, cuda_device, base_models):
+    _, gpu = base_models
+    wl = S.workload("cfg1")
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    b, s = len(wl.lengths), wl.max_seqlen
+    ids = torch.zeros(b, s, dtype=torch.int64)
+    mask = torch.zeros(b, s, dtype=torch.int64)
+    for i, seq in enumerate(wl.sequences()):
+        ids[i, : seq.numel()] = seq
+        mask[i, : seq.numel()] = 1
+    packed = pe.packed_forward(gpu, params, *_packed_inputs(wl, cuda_device))
+    padded = pe.fused_forward(gpu, params, ids.to(cuda_device), mask.to(cuda_device))
+    assert padded.shape == (b, s, 768)
+    assert torch.equal(padded[mask.bool().to(cuda_device)], packed)
+    assert not bool(padded[~mask.bool().to(cuda_device)].ne(0).any())
+
+
+def test_cfg3_full_size_properties(pe, cuda_device, base_models):
+    """The headline workload (512 documents, 306,851 tokens): permutation equivariance over
+    sequences and agreement of a sequence encoded alone with the same sequence in the batch."""
+    from flash_modernbert_b200 import forward
+
+    _, gpu = base_models
+    wl = S.workload("cfg3").sorted_by_length()
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    ids, cu, max_s, pos = _packed_inputs(wl, cuda_device)
+    out = pe.packed_forward(gpu, params, ids, cu, max_s, pos)
+    forward.get_binding(gpu, params).check(sync=True)
+    assert out.shape == (306851, 768) and bool(torch.isfinite(out.float()).all())
+    seqs = wl.sequences()
+    for n in (0, 100, 511):
+        alone = pe.pack_sequences([seqs[n]], device=cuda_device)
+        solo = pe.packed_forward(gpu, params, *alone.forward_args())
+        s, e = int(cu[n]), int(cu[n + 1])
+        rep = O.cosine_report(solo.cpu(), out[s:e].cpu())
+        assert rep["min_token_cos"] > 0.9999, (n, rep)   # only batch-size-dependent tiling differs
+
+
+def test_against_reference_gpu_packed_forward(pe, cuda_device, base_models):
+    """Same seeded inputs through the reference's own GPU packed_forward, when its install
+    (baseline/_ref) and its JIT toolchains work on this machine."""
+    ref_dir = ROOT / "baseline" / "_ref"
+    if not (ref_dir / "packed_encoders").exists():
+        pytest.skip("reference install not present")
+    sys.path.insert(0, str(ref_dir))
+    try:
+        try:
+            from packed_encoders import forward as ref_forward
+            from packed_encoders.config import ModernBertParams as RefParams
+        except Exception as exc:  # noqa: BLE001
+            pytest.skip(f"reference does not import here: {exc}")
+        _, gpu = base_models
+        wl = S.workload("cfg1")
+        ids, cu, max_s, pos = _packed_inputs(wl, cuda_device)
+        cfg = gpu.config
+        if not hasattr(cfg, "global_attn_every_n_layers"):
+            cfg.global_attn_every_n_layers = 3
+        try:
+            with torch.no_grad():
+                ref_out = ref_forward.packed_forward(gpu, RefParams.from_hf_config(cfg), ids, cu, max_s, pos)
+            torch.cuda.synchronize()
+        except Exception as exc:  # noqa: BLE001
+            pytest.skip(f"reference packed_forward does not run here: {type(exc).__name__}: {exc}")
+        params = pe.ModernBertParams.from_hf_config(cfg)
+        out = pe.packed_forward(gpu, params, ids, cu, max_s, pos)
+        rep = O.cosine_report(out.cpu(), ref_out.cpu())
+        print(f"vs reference GPU packed_forward: {rep}")
+        assert rep["min_token_cos"] >= COS_GATE, rep
+    finally:
+        sys.path.remove(str(ref_dir))

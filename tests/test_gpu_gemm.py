@@ -1,0 +1,80 @@
+"""The tcgen05 GEMM against a plain fp32 torch reference, through the C ABI."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import packed_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+# (M, N, K): every projection shape of the base / large / 1B models, plus ragged M
+SHAPES = [
+    (128, 256, 64), (1, 768, 768), (127, 768, 768), (129, 2304, 768), (1000, 768, 1152),
+    (4097, 2304, 768), (300, 3072, 1024), (300, 1024, 2624), (300, 5248, 1024),
+    (200, 5376, 1792), (200, 1792, 3840), (200, 7680, 1792), (77, 8, 8), (513, 72, 200),
+]
+
+
+def _inputs(m, n, k, device, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=gen).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=gen) * 0.05).to(torch.bfloat16)
+    return a, w, a.to(device), w.to(device)
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_gemm_matches_fp32_reference(pe, cuda_device, m, n, k):
+    from flash_modernbert_b200 import ops
+
+    a, w, a_d, w_d = _inputs(m, n, k, cuda_device)
+    out = ops._linear(a_d, w_d)
+    ops.check_status(cuda_device)
+    ref = a_d.float() @ w_d.float().t()           # fp32 reference of the same op
+    got = out.float()
+    # bf16 output of an fp32 accumulation: half a bf16 step of the result plus fp32 summation-order noise
+    tol = ref.abs() * 2 ** -8 + 1e-3 * (k ** 0.5) * 0.05
+    assert bool(((got - ref).abs() <= tol).all()), float((got - ref).abs().max())
+    # tolerance of the reference's own GEMM test (tests/test_matmul.py:49-55)
+    torch.testing.assert_close(out, torch.nn.functional.linear(a_d, w_d), rtol=1e-2, atol=1.0)
+
+
+def test_gemm_is_deterministic_and_handles_empty(pe, cuda_device):
+    from flash_modernbert_b200 import ops
+
+    _, _, a_d, w_d = _inputs(2000, 768, 768, cuda_device, seed=1)
+    assert torch.equal(ops._linear(a_d, w_d), ops._linear(a_d, w_d))
+    empty = ops._linear(a_d[:0], w_d)
+    assert empty.shape == (0, 768)
+    lead = ops._linear(a_d.view(4, 500, 768), w_d)
+    assert lead.shape == (4, 500, 768) and torch.equal(lead.view(2000, 768), ops._linear(a_d, w_d))
+
+
+def test_gemm_linearity_at_full_size(pe, cuda_device):
+    """cfg3-sized M: W (a + b) == W a + W b up to rounding, and row blocks are independent."""
+    from flash_modernbert_b200 import ops
+
+    gen = torch.Generator(device=cuda_device).manual_seed(0)
+    m = 306851
+    a = torch.randn(m, 768, device=cuda_device, generator=gen).to(torch.bfloat16)
+    w = (torch.randn(2304, 768, device=cuda_device, generator=gen) * 0.05).to(torch.bfloat16)
+    full = ops._linear(a, w)
+    ops.check_status(cuda_device)
+    rows = torch.randint(0, m, (4096,), device=cuda_device)
+    ref = a[rows].float() @ w.float().t()
+    assert float((full[rows].float() - ref).abs().max()) < 0.05
+    tail = ops._linear(a[m - 1000:], w)
+    assert torch.equal(tail, full[m - 1000:])
+
+
+@pytest.mark.parametrize("m,inter,k", [(129, 1152, 768), (1000, 1152, 768), (300, 2624, 1024), (200, 3840, 1792), (64, 128, 64)])
+def test_fused_wi_geglu_equals_two_kernels(pe, cuda_device, m, inter, k):
+    from flash_modernbert_b200 import ops
+
+    a, wi, a_d, wi_d = _inputs(m, 2 * inter, k, cuda_device, seed=2)
+    fused = ops.linear_geglu(a_d, wi_d)
+    two = ops.fused_geglu(ops._linear(a_d, wi_d))
+    ops.check_status(cuda_device)
+    assert torch.equal(fused, two)                 # same rounding points => same bits
+    ref = O.geglu(O.linear(a, wi))
+    assert float((fused.cpu().float() - ref).abs().max()) <= 0.02 * float(ref.abs().max()) + 1e-3
