@@ -268,18 +268,18 @@ static int check_gemm_args(const void* A, const void* W, const void* C, int64_t 
 
 extern "C" int pe_gemm_bf16_tn(const void* A, const void* W, void* C, int64_t M, int Nout, int K,
                                int32_t* status, void* stream) {
+  if (M == 0) return PE_OK;
   int rc = pe::check_gemm_args(A, W, C, M, Nout, K, "pe_gemm_bf16_tn");
   if (rc != PE_OK) return rc;
-  if (M == 0) return PE_OK;
   return pe::launch_gemm<false>(A, W, C, M, Nout, K, Nout, 0, status,
                                 static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int pe_gemm_geglu_bf16(const void* A, const void* Wi, void* out, int64_t M, int I, int K,
                                   int32_t* status, void* stream) {
+  if (M == 0) return PE_OK;
   int rc = pe::check_gemm_args(A, Wi, out, M, I, K, "pe_gemm_geglu_bf16");
   if (rc != PE_OK) return rc;
-  if (M == 0) return PE_OK;
   return pe::launch_gemm<true>(A, Wi, out, M, I, K, 2 * I, I, status,
                                static_cast<cudaStream_t>(stream));
 }

@@ -142,12 +142,16 @@ def test_bucketed_cuda_graphs(pe, cuda_device, tiny_models):
         assert runner.captures <= 5 and all(k[1] == 64 and k[2] == 64 for k in runner._cache)
         long_batch = pe.pack_sequences([torch.randint(5, vocab, (100,), generator=gen)], device=cuda_device)
         before = runner.eager_calls
-        pe.packed_forward(gpu, params, *long_batch.forward_args())    # over max_seq: eager
+        with torch.no_grad():
+            pe.packed_forward(gpu, params, *long_batch.forward_args())    # over max_seq: eager
         assert runner.eager_calls == before + 1
+        replays = runner.replays
+        pe.packed_forward(gpu, params, *batch.forward_args())         # autograd on: eager
+        assert runner.replays == replays
         os.environ["PACKED_ENCODERS_GRAPH"] = "0"
         try:
-            replays = runner.replays
-            pe.packed_forward(gpu, params, *batch.forward_args())
+            with torch.no_grad():
+                pe.packed_forward(gpu, params, *batch.forward_args())
             assert runner.replays == replays                          # kill switch
         finally:
             del os.environ["PACKED_ENCODERS_GRAPH"]

@@ -20,15 +20,16 @@ def _bits(t: torch.Tensor) -> torch.Tensor:
     return t.contiguous().view(torch.int16).to(torch.int32)
 
 
-def assert_bf16_close(actual, expected_f32, max_ulp=1, max_frac=0.02, what=""):
+def assert_bf16_close(actual, expected_f32, max_ulp=1, max_frac=0.02, what="", atol=0.0):
     """`actual` bf16 CUDA vs an fp32 CPU tensor of bf16-representable values: equal except
-    for at most `max_frac` of the elements, each within `max_ulp` bf16 steps."""
+    for at most `max_frac` of the elements, each within `max_ulp` bf16 steps (or within
+    `atol` in value, for results that sit next to zero after a cancellation)."""
     a = actual.detach().cpu()
     e = expected_f32.to(torch.bfloat16)
     ulp = (_bits(a) - _bits(e)).abs()
     # bit distance is meaningful where the signs agree; tiny values across zero are compared in value
     same_sign = (a.float() * e.float()) >= 0
-    bad = (ulp > max_ulp) & same_sign
+    bad = (ulp > max_ulp) & same_sign & ((a.float() - e.float()).abs() > atol)
     cross = (~same_sign) & ((a.float() - e.float()).abs() > 1e-2)
     assert not bool(bad.any() or cross.any()), (
         f"{what}: {int(bad.sum())} elements off by more than {max_ulp} ulp; "
@@ -188,4 +189,6 @@ def test_geglu(pe, cuda_device, rows, inter):
     torch.manual_seed(4)
     proj = (torch.randn(rows, 2 * inter) * 2).to(torch.bfloat16)
     out = ops.fused_geglu(proj.to(cuda_device))
-    assert_bf16_close(out, O.geglu(proj), what="geglu")
+    # gelu(a) for a << 0 is a * (1 + erf(..)) with 1 + erf cancelling: device erff and the host's
+    # erf differ in the last bits there, which is far below one bf16 step of any O(1) output
+    assert_bf16_close(out, O.geglu(proj), what="geglu", atol=5e-4)
