@@ -324,7 +324,8 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t* __r
 int attn_pick_bm(int max_seqlen) {
   if (max_seqlen <= 16) return 16;
   if (max_seqlen <= 32) return 32;
-  return 64;
+  if (max_seqlen <= 96) return 64;
+  return 128;  // tensor-memory kernel (attn_tcgen05.cu)
 }
 
 int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int bm, int32_t* tile_start,
@@ -337,7 +338,8 @@ int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int bm, int32_t* tile_s
 int attn_run(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_start, int n_seqs,
              int64_t T, int nh, int half_window, int bm, void* out, int32_t* status,
              cudaStream_t st) {
-  (void)status;
+  if (bm == 128)
+    return attn_run_tc(qkv, cu_seqlens, tile_start, n_seqs, T, nh, half_window, out, status, st);
   // Upper bound on the number of query tiles given only the capacities.
   const int64_t max_tiles = T / bm + n_seqs;
   PE_REQUIRE(max_tiles < (1ll << 31), "attention: too many tiles");

@@ -48,6 +48,10 @@ int attn_run(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_sta
              int64_t T, int nh, int half_window, int bm, void* out, int32_t* status,
              cudaStream_t st);
 
+// The 128-row tensor-memory attention kernel (attn_tcgen05.cu); tile_start built with bm = 128.
+int attn_run_tc(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_start, int n_seqs,
+                int64_t T, int nh, int half_window, void* out, int32_t* status, cudaStream_t st);
+
 // Process-wide switches (pe_set_option).
 enum Option : int { OPT_FUSED_GEGLU = 1, OPT_COUNT };
 int get_option(int key);

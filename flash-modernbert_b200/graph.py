@@ -69,17 +69,19 @@ def _pow2_at_least(value: int) -> int:
 
 
 def query_tile_rows(max_seqlen: int) -> int:
-    """Rows per attention query tile the library picks for a longest length (16/32/64)."""
+    """Rows per attention query tile the library picks for a longest length (16/32/64/128)."""
     if max_seqlen <= 16:
         return 16
     if max_seqlen <= 32:
         return 32
-    return 64
+    if max_seqlen <= 96:
+        return 64
+    return 128
 
 
 def _tile_class_seqlen(rows: int) -> int:
     """A max_seqlen that selects the `rows`-row query tile."""
-    return {16: 16, 32: 32}.get(rows, 1 << 30)
+    return {16: 16, 32: 32, 64: 96}.get(rows, 1 << 30)
 
 
 @dataclass
@@ -204,7 +206,7 @@ class _PackedGraphRunner:
         )
         # A valid stand-in distribution for warm-up and capture: one sequence of
         # min(token_cap, tile class) tokens, everything else empty.
-        first = min(token_cap, tile_rows if tile_rows < 64 else 64)
+        first = min(token_cap, tile_rows)
         static.cu_seqlens[1:].fill_(first)
         static.position_ids[:first] = torch.arange(first, device=dev)
         out = torch.empty(token_cap, self._params.hidden_size, dtype=torch.bfloat16, device=dev)

@@ -131,9 +131,10 @@ def test_bucketed_cuda_graphs(pe, cuda_device, tiny_models):
             lengths = torch.randint(33, 49, (n,), generator=gen).tolist()
             seqs = [torch.randint(5, vocab, (l,), generator=gen) for l in lengths]
             batch = pe.pack_sequences(seqs, device=cuda_device)
-            graphed = pe.packed_forward(gpu, params, *batch.forward_args())
-            with pe.no_cuda_graph(gpu):
-                eager = pe.packed_forward(gpu, params, *batch.forward_args())
+            with torch.no_grad():       # graphs engage only with autograd off, as in the reference
+                graphed = pe.packed_forward(gpu, params, *batch.forward_args())
+                with pe.no_cuda_graph(gpu):
+                    eager = pe.packed_forward(gpu, params, *batch.forward_args())
             forward.get_binding(gpu, params).check(sync=True)
             assert graphed.shape == eager.shape
             assert torch.equal(graphed, eager), trial         # same kernels, same data => same bits

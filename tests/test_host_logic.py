@@ -135,8 +135,8 @@ def test_graph_bucket_policy(pe):
     assert runner.bucket_for(100, 3, 65) is None         # too long
     assert runner.bucket_for(50001, 3, 16) is None       # over max_tokens
     runner._config = pe.GraphConfig(token_buckets=(1024, 4096, 16384))
-    assert runner.bucket_for(1000, 5, 100) == (1024, 8, 64)
-    assert runner.bucket_for(1025, 9, 100) == (4096, 16, 64)
+    assert runner.bucket_for(1000, 5, 100) == (1024, 8, 128)
+    assert runner.bucket_for(1025, 9, 96) == (4096, 16, 64)
     assert runner.bucket_for(16385, 9, 100) is None
 
 
