@@ -2,16 +2,19 @@
 // cores: S = Q K^T and O = P V run as tcgen05.mma with S and O in tensor memory,
 // Q / K / V tiles arrive by TMA straight from the fused qkv [T, 3*nh*64].
 //
-// One CTA owns one (128-query tile, head) and walks 128-key tiles:
+// Persistent CTAs (one per SM) walk work items (128-query tile, head) round-robin;
+// each item walks 128-key tiles.  The three roles keep their own cursors over the
+// same item sequence, so the pipeline never drains between items:
 //   warps 0..3 : softmax - thread t owns query row t (tensor-memory lane t): reads its
 //                128 scores with tcgen05.ld, online softmax in the exp2 domain, writes
 //                P (bf16) into shared memory in the 128-byte-swizzled K-major layout
 //                tcgen05.mma reads, then folds the previous tile's P V into its fp32
-//                output row held in registers
-//   warp 4     : TMA producer - Q once, then K_j and V_j into a 3-stage ring
-//   warp 5     : tensor-memory owner and MMA issuer - S_j = Q K_j^T runs up to two
-//                tiles ahead into a double-buffered S; O_j = P_j V_j goes to a
-//                double-buffered 64-column scratch that the softmax warps drain
+//                output row held in registers; stores the row at the end of the item
+//   warp 4     : TMA producer - Q into a double buffer, K_j and V_j into a 3-stage ring,
+//                running ahead across items as far as the buffers allow
+//   warp 5     : tensor-memory owner and MMA issuer - S = Q K^T runs up to two key tiles
+//                ahead (across item boundaries) into a double-buffered S; O_j = P_j V_j
+//                goes to a double-buffered 64-column scratch that the softmax warps drain
 // Keeping the running output in registers (rather than rescaling an accumulator in
 // tensor memory) means P V never needs a correction pass over tensor memory.
 //
@@ -30,22 +33,51 @@ constexpr int TC_STAGES = 3;
 constexpr int TC_TILE_BYTES = 128 * 64 * 2;          // one 128 x 64 bf16 tile (Q, K or V)
 constexpr int TC_P_BYTES = 128 * 128 * 2;            // one P buffer: two 128 x 64 halves
 constexpr int TC_THREADS = 192;
-constexpr int TC_SMEM = TC_TILE_BYTES * (1 + 2 * TC_STAGES) + 2 * TC_P_BYTES + 1024 + 256;
+constexpr int TC_SMEM = TC_TILE_BYTES * (2 + 2 * TC_STAGES) + 2 * TC_P_BYTES + 1024 + 256;
 constexpr uint32_t TC_TMEM_COLS = 512;
 constexpr uint32_t TC_S_COL = 0;    // S[b] at columns b * 128
 constexpr uint32_t TC_O_COL = 256;  // O[b] at columns 256 + b * 64
 
 // barrier slots
 enum {
-  TCB_Q_FULL = 0,
-  TCB_KV_FULL = 1,    // 3
-  TCB_KV_EMPTY = 4,   // 3
-  TCB_S_FULL = 7,     // 2
-  TCB_S_EMPTY = 9,    // 2
-  TCB_P_FULL = 11,    // 2
-  TCB_O_FULL = 13,    // 2
-  TCB_COUNT = 15
+  TCB_Q_FULL = 0,     // 2
+  TCB_Q_EMPTY = 2,    // 2
+  TCB_KV_FULL = 4,    // 3
+  TCB_KV_EMPTY = 7,   // 3
+  TCB_S_FULL = 10,    // 2
+  TCB_S_EMPTY = 12,   // 2
+  TCB_P_FULL = 14,    // 2
+  TCB_O_FULL = 16,    // 2
+  TCB_COUNT = 18
 };
+
+// One work item: a 128-query tile of one sequence, for one head.
+struct TcItem {
+  int seq_begin, len, q0, head;
+  int kv_start, n_kv;
+};
+
+__device__ __forceinline__ TcItem tc_make_item(const int4 info, int item, int nh, int half_window) {
+  TcItem it;
+  it.seq_begin = info.x;
+  it.len = info.y;
+  it.q0 = info.z;
+  it.head = item % nh;
+  // key tile j covers keys [kv_start + 128 j, kv_start + 128 j + 128) of the sequence
+  it.kv_start = 0;
+  it.n_kv = (it.len + TC_BN - 1) / TC_BN;
+  if (half_window >= 0) {
+    it.kv_start = it.q0 - half_window;  // may be negative: those keys are masked
+    const int kv_end = min(it.len, it.q0 + TC_BM + half_window);
+    it.n_kv = (kv_end - it.kv_start + TC_BN - 1) / TC_BN;
+  }
+  return it;
+}
+
+__device__ __forceinline__ TcItem tc_load_item(const int4* __restrict__ tile_info, int item, int nh,
+                                               int half_window) {
+  return tc_make_item(__ldg(tile_info + item / nh), item, nh, half_window);
+}
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -68,57 +100,38 @@ __device__ __forceinline__ void tmem_ld_32x32_nowait(uint32_t taddr, uint32_t* v
 }
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
-attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
-                      const int32_t* __restrict__ cu_seqlens,
-                      const int32_t* __restrict__ tile_start, int n_seqs, int nh, int half_window,
+attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __restrict__ tile_info,
+                      const int32_t* __restrict__ total_tiles_ptr, int nh, int half_window,
                       __nv_bfloat16* __restrict__ out, int* status) {
-  const int total_tiles = tile_start[n_seqs];
-  const int tile = blockIdx.x;
-  if (tile >= total_tiles) return;  // whole CTA leaves before any barrier or allocation
+  const int total_items = *total_tiles_ptr * nh;
+  if (int(blockIdx.x) >= total_items) return;  // whole CTA leaves before any barrier or allocation
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base;
-  const uint32_t sKV = sQ + TC_TILE_BYTES;                       // stage s: K at +0, V at +16 KB
+  const uint32_t sQ = base;                                      // Q[qb] at + qb * 16 KB
+  const uint32_t sKV = sQ + 2 * TC_TILE_BYTES;                   // stage s: K at +0, V at +16 KB
   const uint32_t sP = sKV + 2 * TC_STAGES * TC_TILE_BYTES;       // P[b] at + b * 32 KB
   const uint32_t bar_base = sP + 2 * TC_P_BYTES;
   auto bar = [&](int i) { return bar_base + 8u * i; };
   const uint32_t tmem_slot = bar_base + 8u * TCB_COUNT;
 
-  int lo = 0, hi = n_seqs;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (tile_start[mid] <= tile) lo = mid; else hi = mid;
-  }
-  const int seq = lo;
-  const int seq_begin = cu_seqlens[seq];
-  const int len = cu_seqlens[seq + 1] - seq_begin;
-  const int q0 = (tile - tile_start[seq]) * TC_BM;
-  const int head = blockIdx.y;
-  const int H = nh * 64;
-
-  // key tiles: tile j covers keys [kv_start + 128 j, kv_start + 128 j + 128) of the sequence
-  int kv_start = 0, n_kv = (len + TC_BN - 1) / TC_BN;
-  if (half_window >= 0) {
-    kv_start = q0 - half_window;  // may be negative: those keys are masked
-    const int kv_end = min(len, q0 + TC_BM + half_window);
-    n_kv = (kv_end - kv_start + TC_BN - 1) / TC_BN;
-  }
-
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int H = nh * 64;
+  const int stride_items = gridDim.x;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(TCB_Q_FULL), 1);
-    for (int s = 0; s < TC_STAGES; ++s) {
-      mbar_init(bar(TCB_KV_FULL + s), 1);
-      mbar_init(bar(TCB_KV_EMPTY + s), 1);
-    }
     for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(TCB_Q_FULL + b), 1);
+      mbar_init(bar(TCB_Q_EMPTY + b), 1);
       mbar_init(bar(TCB_S_FULL + b), 1);
       mbar_init(bar(TCB_S_EMPTY + b), 4);
       mbar_init(bar(TCB_P_FULL + b), 128);
       mbar_init(bar(TCB_O_FULL + b), 1);
+    }
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(bar(TCB_KV_FULL + s), 1);
+      mbar_init(bar(TCB_KV_EMPTY + s), 1);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tm_qkv);
@@ -136,18 +149,28 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
   if (warp == 4) {
     // ---------------------------------------------------------------- TMA producer
     if (elect_one()) {
-      const int qcol = head * 64, kcol = H + head * 64, vcol = 2 * H + head * 64;
-      mbar_expect_tx(bar(TCB_Q_FULL), TC_TILE_BYTES);
-      tma_load_2d(sQ, &tm_qkv, bar(TCB_Q_FULL), qcol, seq_begin + q0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j % TC_STAGES;
-        const uint32_t ph = (j / TC_STAGES) & 1;
-        if (!mbar_wait(bar(TCB_KV_EMPTY + s), ph ^ 1u, status, ST_ATTN_TIMEOUT)) break;
-        const uint32_t dst = sKV + s * 2 * TC_TILE_BYTES;
-        const int row = seq_begin + kv_start + j * TC_BN;
-        mbar_expect_tx(bar(TCB_KV_FULL + s), 2 * TC_TILE_BYTES);
-        tma_load_2d(dst, &tm_qkv, bar(TCB_KV_FULL + s), kcol, row);
-        tma_load_2d(dst + TC_TILE_BYTES, &tm_qkv, bar(TCB_KV_FULL + s), vcol, row);
+      uint32_t g = 0;  // key tiles loaded so far (ring position)
+      uint32_t n = 0;  // items started so far (Q buffer position)
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < total_items; item += stride_items, ++n) {
+        const TcItem it = tc_load_item(tile_info, item, nh, half_window);
+        const int qcol = it.head * 64, kcol = H + qcol, vcol = 2 * H + qcol;
+        const uint32_t qb = n & 1;
+        if (!mbar_wait(bar(TCB_Q_EMPTY + qb), ((n >> 1) & 1) ^ 1u, status, ST_ATTN_TIMEOUT)) break;
+        mbar_expect_tx(bar(TCB_Q_FULL + qb), TC_TILE_BYTES);
+        tma_load_2d(sQ + qb * TC_TILE_BYTES, &tm_qkv, bar(TCB_Q_FULL + qb), qcol, it.seq_begin + it.q0);
+        for (int j = 0; j < it.n_kv; ++j, ++g) {
+          const uint32_t s = g % TC_STAGES;
+          if (!mbar_wait(bar(TCB_KV_EMPTY + s), ((g / TC_STAGES) & 1) ^ 1u, status, ST_ATTN_TIMEOUT)) {
+            ok = false;
+            break;
+          }
+          const uint32_t dst = sKV + s * 2 * TC_TILE_BYTES;
+          const int row = it.seq_begin + it.kv_start + j * TC_BN;
+          mbar_expect_tx(bar(TCB_KV_FULL + s), 2 * TC_TILE_BYTES);
+          tma_load_2d(dst, &tm_qkv, bar(TCB_KV_FULL + s), kcol, row);
+          tma_load_2d(dst + TC_TILE_BYTES, &tm_qkv, bar(TCB_KV_FULL + s), vcol, row);
+        }
       }
     }
     __syncwarp();
@@ -156,150 +179,177 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
     if (elect_one()) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 64, 1);  // B (= V) is MN-major
-      bool ok = mbar_wait(bar(TCB_Q_FULL), 0, status, ST_ATTN_MMA_TIMEOUT);
-      const uint64_t qdesc = umma_smem_desc_sw128(sQ, 1024);
-
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j % TC_STAGES, b = j & 1;
-        if (!mbar_wait(bar(TCB_KV_FULL + s), (j / TC_STAGES) & 1, status, ST_ATTN_MMA_TIMEOUT))
-          return false;
-        if (!mbar_wait(bar(TCB_S_EMPTY + b), ((j >> 1) & 1) ^ 1u, status, ST_ATTN_MMA_TIMEOUT))
-          return false;
-        tc_fence_after();
-        const uint64_t kdesc = umma_smem_desc_sw128(sKV + s * 2 * TC_TILE_BYTES, 1024);
+      // Two cursors over the same flat sequence of key tiles: `q` issues S = Q K^T,
+      // `p` issues O = P V; q runs at most two tiles ahead of p.
+      int q_item = blockIdx.x, q_j = 0, q_nkv = 0;
+      int p_item = blockIdx.x, p_j = 0, p_nkv = 0;
+      uint32_t gq = 0, gp = 0, nq = 0;  // tiles issued by q / by p, items begun by q
+      if (q_item < total_items) q_nkv = tc_load_item(tile_info, q_item, nh, half_window).n_kv;
+      p_nkv = q_nkv;
+      bool ok = true;
+      while (ok && p_item < total_items) {
+        while (ok && gq < gp + 2 && q_item < total_items) {
+          const uint32_t s = gq % TC_STAGES, b = gq & 1, qb = nq & 1;
+          if (q_j == 0) ok = mbar_wait(bar(TCB_Q_FULL + qb), (nq >> 1) & 1, status, ST_ATTN_MMA_TIMEOUT);
+          ok = ok && mbar_wait(bar(TCB_KV_FULL + s), (gq / TC_STAGES) & 1, status, ST_ATTN_MMA_TIMEOUT);
+          ok = ok && mbar_wait(bar(TCB_S_EMPTY + b), ((gq >> 1) & 1) ^ 1u, status, ST_ATTN_MMA_TIMEOUT);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t qdesc = umma_smem_desc_sw128(sQ + qb * TC_TILE_BYTES, 1024);
+          const uint64_t kdesc = umma_smem_desc_sw128(sKV + s * 2 * TC_TILE_BYTES, 1024);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tmem_base + TC_S_COL + b * 128, qdesc + 2u * kk, kdesc + 2u * kk, idesc_qk,
-                  kk != 0 ? 1u : 0u);
-        umma_commit(bar(TCB_S_FULL + b));
-        return true;
-      };
-
-      for (int j = 0; ok && j < min(2, n_kv); ++j) ok = issue_qk(j);
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const int s = j % TC_STAGES, b = j & 1;
-        if (!mbar_wait(bar(TCB_P_FULL + b), (j >> 1) & 1, status, ST_ATTN_MMA_TIMEOUT)) break;
-        tc_fence_after();
-        const uint32_t pbase = sP + b * TC_P_BYTES;
-        const uint32_t vbase = sKV + s * 2 * TC_TILE_BYTES + TC_TILE_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          // A: keys [16 kk, 16 kk + 16) of P = half kk / 4, 32-byte step kk % 4 inside the atom
-          const uint64_t pdesc =
-              umma_smem_desc_sw128(pbase + (kk >> 2) * TC_TILE_BYTES, 1024) + 2u * (kk & 3);
-          // B: V rows [16 kk, 16 kk + 16), 128 bytes per row
-          const uint64_t vdesc = umma_smem_desc_sw128(vbase + kk * 2048, 1024);
-          umma_ss(tmem_base + TC_O_COL + b * 64, pdesc, vdesc, idesc_pv, kk != 0 ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(tmem_base + TC_S_COL + b * 128, qdesc + 2u * kk, kdesc + 2u * kk, idesc_qk,
+                    kk != 0 ? 1u : 0u);
+          umma_commit(bar(TCB_S_FULL + b));
+          ++gq;
+          if (++q_j == q_nkv) {  // last key tile of the item: its Q buffer is free once these MMAs retire
+            umma_commit(bar(TCB_Q_EMPTY + qb));
+            ++nq;
+            q_item += stride_items;
+            q_j = 0;
+            if (q_item < total_items) q_nkv = tc_load_item(tile_info, q_item, nh, half_window).n_kv;
+          }
         }
-        umma_commit(bar(TCB_O_FULL + b));
-        umma_commit(bar(TCB_KV_EMPTY + s));
-        if (j + 2 < n_kv) ok = issue_qk(j + 2);
+        if (!ok) break;
+        {
+          const uint32_t s = gp % TC_STAGES, b = gp & 1;
+          if (!mbar_wait(bar(TCB_P_FULL + b), (gp >> 1) & 1, status, ST_ATTN_MMA_TIMEOUT)) break;
+          tc_fence_after();
+          const uint32_t pbase = sP + b * TC_P_BYTES;
+          const uint32_t vbase = sKV + s * 2 * TC_TILE_BYTES + TC_TILE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            // A: keys [16 kk, 16 kk + 16) of P = half kk / 4, 32-byte step kk % 4 inside the atom
+            const uint64_t pdesc =
+                umma_smem_desc_sw128(pbase + (kk >> 2) * TC_TILE_BYTES, 1024) + 2u * (kk & 3);
+            // B: V rows [16 kk, 16 kk + 16), 128 bytes per row
+            const uint64_t vdesc = umma_smem_desc_sw128(vbase + kk * 2048, 1024);
+            umma_ss(tmem_base + TC_O_COL + b * 64, pdesc, vdesc, idesc_pv, kk != 0 ? 1u : 0u);
+          }
+          umma_commit(bar(TCB_O_FULL + b));
+          umma_commit(bar(TCB_KV_EMPTY + s));
+          ++gp;
+          if (++p_j == p_nkv) {
+            p_item += stride_items;
+            p_j = 0;
+            if (p_item < total_items) p_nkv = tc_load_item(tile_info, p_item, nh, half_window).n_kv;
+          }
+        }
       }
     }
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- softmax warps
     const int row = warp * 32 + lane;       // query row in the tile == tensor-memory lane
-    const int qi = q0 + row;                // position in the sequence
     const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16);
     const float scale_log2 = 0.125f * 1.4426950408889634f;
-    float acc[64];
-#pragma unroll
-    for (int d = 0; d < 64; ++d) acc[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    // valid keys of this row, in sequence coordinates (empty for rows past the end)
-    int key_lo = 0, key_hi = len - 1;
-    if (half_window >= 0) {
-      key_lo = max(0, qi - half_window);
-      key_hi = min(len - 1, qi + half_window);
-    }
-    if (qi >= len) key_hi = -1;
+    uint32_t g = 0;  // key tiles consumed so far
     bool ok = true;
-
-    for (int j = 0; j < n_kv; ++j) {
-      const int b = j & 1;
-      if (!mbar_wait(bar(TCB_S_FULL + b), (j >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) {
-        ok = false;
-        break;
+    int4 info = __ldg(tile_info + blockIdx.x / nh);
+    for (int item = blockIdx.x; ok && item < total_items; item += stride_items) {
+      const TcItem it = tc_make_item(info, item, nh, half_window);
+      if (item + stride_items < total_items)  // next item's descriptor, in flight during this one
+        info = __ldg(tile_info + (item + stride_items) / nh);
+      const int qi = it.q0 + row;  // position in the sequence
+      float acc[64];
+#pragma unroll
+      for (int d = 0; d < 64; ++d) acc[d] = 0.f;
+      float m_run = -INFINITY, l_run = 0.f;
+      // valid keys of this row, in sequence coordinates (empty for rows past the end)
+      int key_lo = 0, key_hi = it.len - 1;
+      if (half_window >= 0) {
+        key_lo = max(0, qi - half_window);
+        key_hi = min(it.len - 1, qi + half_window);
       }
-      tc_fence_after();
-      uint32_t sv[128];
-      const uint32_t s_addr = lane_addr + TC_S_COL + b * 128;
-      tmem_ld_32x32_nowait(s_addr, sv);
-      tmem_ld_32x32_nowait(s_addr + 32, sv + 32);
-      tmem_ld_32x32_nowait(s_addr + 64, sv + 64);
-      tmem_ld_32x32_nowait(s_addr + 96, sv + 96);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(TCB_S_EMPTY + b));
+      if (qi >= it.len) key_hi = -1;
 
-      const int tile_key0 = kv_start + j * TC_BN;
-      const int c_lo = key_lo - tile_key0, c_hi = key_hi - tile_key0;  // valid columns [c_lo, c_hi]
-      const bool full = (c_lo <= 0) && (c_hi >= TC_BN - 1);
-      float mx = -INFINITY;
-      if (full) {
-#pragma unroll
-        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
-      } else {
-#pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          const float v = (c >= c_lo && c <= c_hi) ? __uint_as_float(sv[c]) : -INFINITY;
-          sv[c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
-      }
-      const float m_new = fmaxf(m_run, mx * scale_log2);
-      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = ex2(m_run - m_safe);
-      float sum = 0.f;
-      const uint32_t prow = sP + b * TC_P_BYTES + row * 128;
-#pragma unroll
-      for (int c8 = 0; c8 < 16; ++c8) {  // 16 chunks of 8 keys = 16 bytes of bf16
-        float p[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          p[e] = ex2(fmaf(__uint_as_float(sv[c8 * 8 + e]), scale_log2, -m_safe));
-          sum += p[e];
-        }
-        const uint32_t addr = prow + (c8 >> 3) * TC_TILE_BYTES + (((c8 & 7) ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
-                     "r"(pack_bf16(p[0], p[1])), "r"(pack_bf16(p[2], p[3])),
-                     "r"(pack_bf16(p[4], p[5])), "r"(pack_bf16(p[6], p[7]))
-                     : "memory");
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(bar(TCB_P_FULL + b));
-
-      if (j > 0) {  // fold in the previous tile's P V, then move to the new running maximum
-        const int pb = b ^ 1;
-        if (!mbar_wait(bar(TCB_O_FULL + pb), ((j - 1) >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) {
+      for (int j = 0; j < it.n_kv; ++j, ++g) {
+        const uint32_t b = g & 1;
+        if (!mbar_wait(bar(TCB_S_FULL + b), (g >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        uint32_t ov[64];
-        tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64, ov);
-        tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64 + 32, ov + 32);
+        uint32_t sv[128];
+        const uint32_t s_addr = lane_addr + TC_S_COL + b * 128;
+        tmem_ld_32x32_nowait(s_addr, sv);
+        tmem_ld_32x32_nowait(s_addr + 32, sv + 32);
+        tmem_ld_32x32_nowait(s_addr + 64, sv + 64);
+        tmem_ld_32x32_nowait(s_addr + 96, sv + 96);
         tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(TCB_S_EMPTY + b));
+
+        const int tile_key0 = it.kv_start + j * TC_BN;
+        const int c_lo = key_lo - tile_key0, c_hi = key_hi - tile_key0;  // valid columns [c_lo, c_hi]
+        const bool full = (c_lo <= 0) && (c_hi >= TC_BN - 1);
+        float mx = -INFINITY;
+        if (full) {
 #pragma unroll
-        for (int d = 0; d < 64; ++d) acc[d] = (acc[d] + __uint_as_float(ov[d])) * alpha;
+          for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 128; ++c) {
+            const float v = (c >= c_lo && c <= c_hi) ? __uint_as_float(sv[c]) : -INFINITY;
+            sv[c] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+        }
+        const float m_new = fmaxf(m_run, mx * scale_log2);
+        const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = ex2(m_run - m_safe);
+        float sum = 0.f;
+        const uint32_t prow = sP + b * TC_P_BYTES + row * 128;
+#pragma unroll
+        for (int c8 = 0; c8 < 16; ++c8) {  // 16 chunks of 8 keys = 16 bytes of bf16
+          float p[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            p[e] = ex2(fmaf(__uint_as_float(sv[c8 * 8 + e]), scale_log2, -m_safe));
+            sum += p[e];
+          }
+          const uint32_t addr = prow + (c8 >> 3) * TC_TILE_BYTES + (((c8 & 7) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                       "r"(pack_bf16(p[0], p[1])), "r"(pack_bf16(p[2], p[3])),
+                       "r"(pack_bf16(p[4], p[5])), "r"(pack_bf16(p[6], p[7]))
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bar(TCB_P_FULL + b));
+
+        if (j > 0) {  // fold in the previous tile's P V, then move to the new running maximum
+          const uint32_t pb = b ^ 1;
+          if (!mbar_wait(bar(TCB_O_FULL + pb), ((g - 1) >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint32_t ov[64];
+          tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64, ov);
+          tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64 + 32, ov + 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int d = 0; d < 64; ++d) acc[d] = (acc[d] + __uint_as_float(ov[d])) * alpha;
+        }
+        l_run = l_run * alpha + sum;
+        m_run = m_new;
       }
-      l_run = l_run * alpha + sum;
-      m_run = m_new;
-    }
-    if (ok && n_kv > 0) {
-      const int pb = (n_kv - 1) & 1;
-      if (mbar_wait(bar(TCB_O_FULL + pb), ((n_kv - 1) >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) {
+      if (!ok) break;
+      {  // last tile's P V, normalise, store the row
+        const uint32_t pb = (g - 1) & 1;
+        if (!mbar_wait(bar(TCB_O_FULL + pb), ((g - 1) >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) break;
         tc_fence_after();
         uint32_t ov[64];
         tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64, ov);
         tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64 + 32, ov + 32);
         tmem_ld_wait();
-        if (qi < len) {
+        tc_fence_before();
+        if (qi < it.len) {
           const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-          __nv_bfloat16* orow = out + (int64_t(seq_begin) + qi) * H + head * 64;
+          __nv_bfloat16* orow = out + (int64_t(it.seq_begin) + qi) * H + it.head * 64;
 #pragma unroll
           for (int d8 = 0; d8 < 8; ++d8) {
             float o[8];
@@ -325,7 +375,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
   }
 }
 
-int attn_run_tc(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_start, int n_seqs,
+int attn_run_tc(const void* qkv, const int4* tile_info, const int32_t* total_tiles, int64_t max_tiles,
                 int64_t T, int nh, int half_window, void* out, int32_t* status, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
@@ -337,11 +387,10 @@ int attn_run_tc(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_
   int rc = make_tmap_bf16_2d(&tm, qkv, (uint64_t)T, (uint64_t)(3 * nh * 64), (uint64_t)(3 * nh * 64),
                              128);
   if (rc != PE_OK) return rc;
-  const int64_t max_tiles = T / TC_BM + n_seqs;
-  PE_REQUIRE(max_tiles < (1ll << 31), "attention: too many tiles");
-  dim3 grid((unsigned)max_tiles, (unsigned)nh);
+  const int64_t max_items = max_tiles * nh;
+  const int grid = (int)(max_items < sm_count() ? max_items : sm_count());
   attn_varlen_tc_kernel<<<grid, TC_THREADS, TC_SMEM, st>>>(
-      tm, cu_seqlens, tile_start, n_seqs, nh, half_window, static_cast<__nv_bfloat16*>(out), status);
+      tm, tile_info, total_tiles, nh, half_window, static_cast<__nv_bfloat16*>(out), status);
   PE_LAUNCH_CHECK("attn_varlen_tc_kernel");
   return PE_OK;
 }

@@ -23,8 +23,9 @@ constexpr int ATT_BN = 64;  // keys per tile
 constexpr int ATT_D = 64;
 
 // tile_start[n] = number of query tiles of sequences 0..n-1; tile_start[n_seqs] = total.
+// tile_info[t] = {first token of the sequence, sequence length, first query row of the tile, sequence}.
 __global__ void attn_schedule_kernel(const int32_t* __restrict__ cu_seqlens, int n_seqs, int bm,
-                                     int32_t* __restrict__ tile_start) {
+                                     int32_t* __restrict__ tile_start, int4* __restrict__ tile_info) {
   __shared__ int warp_sums[32];
   __shared__ int carry_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -64,6 +65,15 @@ __global__ void attn_schedule_kernel(const int32_t* __restrict__ cu_seqlens, int
     __syncthreads();
     if (threadIdx.x == 0) carry_s = carry + warp_sums[(blockDim.x >> 5) - 1];
     __syncthreads();
+  }
+  __threadfence_block();
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_seqs; i += blockDim.x) {
+    const int begin = cu_seqlens[i];
+    const int len = cu_seqlens[i + 1] - begin;
+    const int first = tile_start[i];
+    const int n = tile_start[i + 1] - first;
+    for (int t = 0; t < n; ++t) tile_info[first + t] = make_int4(begin, len, t * bm, i);
   }
 }
 
@@ -123,8 +133,8 @@ __device__ __forceinline__ void load_tile_async(uint32_t smem_tile, const __nv_b
 
 template <int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
-attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t* __restrict__ cu_seqlens,
-                       const int32_t* __restrict__ tile_start, int n_seqs, int nh, int half_window,
+attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __restrict__ tile_info,
+                       const int32_t* __restrict__ total_tiles_ptr, int nh, int half_window,
                        __nv_bfloat16* __restrict__ out) {
   constexpr int BM = NWARPS * 16;
   constexpr int THREADS = NWARPS * 32;
@@ -133,19 +143,12 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int32_t* __r
   const uint32_t sK = sQ + BM * 128;
   const uint32_t sV = sK + 2 * ATT_BN * 128;
 
-  const int total_tiles = tile_start[n_seqs];
   const int tile = blockIdx.x;
-  if (tile >= total_tiles) return;
-  // Sequence owning this tile: last n with tile_start[n] <= tile.
-  int lo = 0, hi = n_seqs;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (tile_start[mid] <= tile) lo = mid; else hi = mid;
-  }
-  const int seq = lo;
-  const int seq_begin = cu_seqlens[seq];
-  const int len = cu_seqlens[seq + 1] - seq_begin;
-  const int q0 = (tile - tile_start[seq]) * BM;
+  if (tile >= *total_tiles_ptr) return;
+  const int4 info = tile_info[tile];
+  const int seq_begin = info.x;
+  const int len = info.y;
+  const int q0 = info.z;
   const int head = blockIdx.y;
   const int H = nh * ATT_D;
   const int64_t stride = 3 * int64_t(H);
@@ -328,33 +331,44 @@ int attn_pick_bm(int max_seqlen) {
   return 128;  // tensor-memory kernel (attn_tcgen05.cu)
 }
 
-int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int bm, int32_t* tile_start,
-                  cudaStream_t st) {
-  attn_schedule_kernel<<<1, 1024, 0, st>>>(cu_seqlens, n_seqs, bm, tile_start);
+// Scratch layout: tile_start int32[n_seqs + 1], padded to 16 bytes, then tile_info int4[max tiles].
+static size_t info_offset(int n_seqs) { return (size_t(n_seqs + 2) * sizeof(int32_t) + 15) & ~size_t(15); }
+
+size_t attn_scratch_bytes(int64_t T, int n_seqs) {
+  return info_offset(n_seqs) + size_t(T / 16 + n_seqs + 1) * sizeof(int4);
+}
+
+int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int bm, void* scratch, cudaStream_t st) {
+  int32_t* tile_start = static_cast<int32_t*>(scratch);
+  int4* tile_info = reinterpret_cast<int4*>(static_cast<uint8_t*>(scratch) + info_offset(n_seqs));
+  attn_schedule_kernel<<<1, 1024, 0, st>>>(cu_seqlens, n_seqs, bm, tile_start, tile_info);
   PE_LAUNCH_CHECK("attn_schedule_kernel");
   return PE_OK;
 }
 
-int attn_run(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_start, int n_seqs,
-             int64_t T, int nh, int half_window, int bm, void* out, int32_t* status,
-             cudaStream_t st) {
-  if (bm == 128)
-    return attn_run_tc(qkv, cu_seqlens, tile_start, n_seqs, T, nh, half_window, out, status, st);
+int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh, int half_window,
+             int bm, void* out, int32_t* status, cudaStream_t st) {
+  const int32_t* tile_start = static_cast<const int32_t*>(scratch);
+  const int4* tile_info =
+      reinterpret_cast<const int4*>(static_cast<const uint8_t*>(scratch) + info_offset(n_seqs));
+  const int32_t* total_ptr = tile_start + n_seqs;
   // Upper bound on the number of query tiles given only the capacities.
   const int64_t max_tiles = T / bm + n_seqs;
   PE_REQUIRE(max_tiles < (1ll << 31), "attention: too many tiles");
+  if (bm == 128)
+    return attn_run_tc(qkv, tile_info, total_ptr, max_tiles, T, nh, half_window, out, status, st);
   dim3 grid((unsigned)max_tiles, (unsigned)nh);
   const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(qkv);
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   switch (bm) {
     case 16:
-      attn_varlen_mma_kernel<1><<<grid, 32, 0, st>>>(q, cu_seqlens, tile_start, n_seqs, nh, half_window, o);
+      attn_varlen_mma_kernel<1><<<grid, 32, 0, st>>>(q, tile_info, total_ptr, nh, half_window, o);
       break;
     case 32:
-      attn_varlen_mma_kernel<2><<<grid, 64, 0, st>>>(q, cu_seqlens, tile_start, n_seqs, nh, half_window, o);
+      attn_varlen_mma_kernel<2><<<grid, 64, 0, st>>>(q, tile_info, total_ptr, nh, half_window, o);
       break;
     case 64:
-      attn_varlen_mma_kernel<4><<<grid, 128, 0, st>>>(q, cu_seqlens, tile_start, n_seqs, nh, half_window, o);
+      attn_varlen_mma_kernel<4><<<grid, 128, 0, st>>>(q, tile_info, total_ptr, nh, half_window, o);
       break;
     default:
       set_last_error("attention: unsupported query tile %d", bm);
@@ -367,8 +381,8 @@ int attn_run(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_sta
 }  // namespace pe
 
 extern "C" size_t pe_attn_workspace_bytes(int64_t T, int n_seqs) {
-  (void)T;
-  return (size_t(n_seqs) + 2) * sizeof(int32_t);
+  if (T < 0 || n_seqs < 0) return 0;
+  return pe::attn_scratch_bytes(T, n_seqs);
 }
 
 extern "C" int pe_attn_varlen(const void* qkv, const int32_t* cu_seqlens, int n_seqs, int64_t T,
@@ -378,6 +392,8 @@ extern "C" int pe_attn_varlen(const void* qkv, const int32_t* cu_seqlens, int n_
   PE_REQUIRE(qkv && cu_seqlens && out && workspace, "pe_attn_varlen: null pointer");
   PE_REQUIRE(n_seqs > 0 && T >= 0 && nh > 0 && nh <= 65535, "pe_attn_varlen: bad sizes");
   PE_REQUIRE(max_seqlen > 0, "pe_attn_varlen: max_seqlen must be positive");
+  PE_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+             "pe_attn_varlen: workspace must be 16-byte aligned");
   if (workspace_bytes < pe_attn_workspace_bytes(T, n_seqs)) {
     set_last_error("pe_attn_varlen: workspace %zu < %zu bytes", workspace_bytes,
                    pe_attn_workspace_bytes(T, n_seqs));
@@ -385,9 +401,8 @@ extern "C" int pe_attn_varlen(const void* qkv, const int32_t* cu_seqlens, int n_
   }
   if (T == 0) return PE_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int32_t* tile_start = static_cast<int32_t*>(workspace);
   const int bm = attn_pick_bm(max_seqlen);
-  int rc = attn_schedule(cu_seqlens, n_seqs, bm, tile_start, st);
+  int rc = attn_schedule(cu_seqlens, n_seqs, bm, workspace, st);
   if (rc != PE_OK) return rc;
-  return attn_run(qkv, cu_seqlens, tile_start, n_seqs, T, nh, half_window, bm, out, status, st);
+  return attn_run(qkv, workspace, n_seqs, T, nh, half_window, bm, out, status, st);
 }

@@ -100,7 +100,7 @@ extern "C" int pe_forward_packed(const pe_model* model, const int64_t* ids,
   void* tmp = ws + w.tmp;
   void* act = ws + w.act;
   void* proj = ws + w.proj;
-  int32_t* tiles = reinterpret_cast<int32_t*>(ws + w.tiles);
+  void* tiles = ws + w.tiles;
   const int H = model->hidden, I = model->intermediate, nh = model->n_heads;
   const float eps = model->eps;
 
@@ -128,8 +128,8 @@ extern "C" int pe_forward_packed(const pe_model* model, const int64_t* ids,
     PE_TRY(pe_gemm_bf16_tn(attn_in, L.wqkv, qkv, T, 3 * H, H, status, st));
     PE_TRY(pe_rope_qk_inplace(qkv, position_ids, L.is_global ? model->rope_global : model->rope_local,
                               model->max_positions, T, nh, status, st));
-    PE_TRY(attn_run(qkv, cu_seqlens, tiles, n_seqs, T, nh, L.is_global ? -1 : model->half_window, bm,
-                    ctx, status, st));
+    PE_TRY(attn_run(qkv, tiles, n_seqs, T, nh, L.is_global ? -1 : model->half_window, bm, ctx, status,
+                    st));
     PE_TRY(pe_gemm_bf16_tn(ctx, L.wo, tmp, T, H, H, status, st));
     PE_TRY(pe_add_ln(x, tmp, L.mlp_norm_w, eps, T, H, x, normed, st));
     if (get_option(OPT_FUSED_GEGLU)) {

@@ -40,16 +40,14 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
                       uint64_t row_stride_elts, uint32_t box_rows);
 
 // Attention in two steps so that a forward builds the query-tile table once and
-// reuses it for every layer (attn_varlen.cu).
+// reuses it for every layer (attn_varlen.cu).  `scratch` holds pe_attn_workspace_bytes.
 int attn_pick_bm(int max_seqlen);
-int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int bm, int32_t* tile_start,
-                  cudaStream_t st);
-int attn_run(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_start, int n_seqs,
-             int64_t T, int nh, int half_window, int bm, void* out, int32_t* status,
-             cudaStream_t st);
-
-// The 128-row tensor-memory attention kernel (attn_tcgen05.cu); tile_start built with bm = 128.
-int attn_run_tc(const void* qkv, const int32_t* cu_seqlens, const int32_t* tile_start, int n_seqs,
+size_t attn_scratch_bytes(int64_t T, int n_seqs);
+int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int bm, void* scratch, cudaStream_t st);
+int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh, int half_window,
+             int bm, void* out, int32_t* status, cudaStream_t st);
+// The persistent 128-row tensor-memory kernel (attn_tcgen05.cu); tiles built with bm = 128.
+int attn_run_tc(const void* qkv, const int4* tile_info, const int32_t* total_tiles, int64_t max_tiles,
                 int64_t T, int nh, int half_window, void* out, int32_t* status, cudaStream_t st);
 
 // Process-wide switches (pe_set_option).
