@@ -346,8 +346,9 @@ def run_ours(args) -> None:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (seeded lengths and token ids, random-init weights normal(0, 0.02))",
         "config": {
-            "workload": f"{args.workload}: ModernBERT-base, 512 documents per GPU, lengths lognormal(median 400, "
-                        f"sigma 0.8) clipped to [64, 8192], packed by cu_seqlens, length-descending",
+            "workload": f"{args.workload}: ModernBERT-{arch}, {len(lengths) // world} sequences per GPU "
+                        f"(cfg3 = documents, lengths lognormal(median 400, sigma 0.8) clipped to [64, 8192]), "
+                        f"packed by cu_seqlens, length-descending",
             "tokens_per_gpu": [int(t) for t in plan.tokens_per_rank],
             "global_tokens": total_tokens, "sequences": len(lengths),
             "parallelism": f"dp{world}: one replica per GPU, cost-balanced document groups, NCCL gather of [T, H]",

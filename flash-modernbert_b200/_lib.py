@@ -29,6 +29,7 @@ _ERR_NAMES = {
     PE_ERR_UNSUPPORTED: "PE_ERR_UNSUPPORTED",
 }
 OPT_FUSED_GEGLU = 1
+OPT_FUSED_ROPE = 2
 
 
 class NativeLibraryError(PackedEncodersError):
@@ -91,6 +92,8 @@ PROTOTYPES = {
                                 c_void_p]),
     "pe_gemm_geglu_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                                    c_void_p]),
+    "pe_gemm_qkv_rope_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
+                                      c_void_p, c_int, c_void_p, c_void_p]),
     "pe_attn_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "pe_attn_varlen": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p,
                                c_void_p, c_size_t, c_void_p, c_void_p]),

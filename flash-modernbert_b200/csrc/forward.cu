@@ -6,7 +6,7 @@
 
 namespace pe {
 
-static int g_options[OPT_COUNT] = {0, /*OPT_FUSED_GEGLU*/ 1};
+static int g_options[OPT_COUNT] = {0, /*OPT_FUSED_GEGLU*/ 1, /*OPT_FUSED_ROPE*/ 1};
 
 int get_option(int key) { return (key > 0 && key < OPT_COUNT) ? g_options[key] : 0; }
 
@@ -125,9 +125,14 @@ extern "C" int pe_forward_packed(const pe_model* model, const int64_t* ids,
       if (pending) PE_TRY(pe_add_ln(x, tmp, nullptr, eps, T, H, x, nullptr, st));
       attn_in = x;
     }
-    PE_TRY(pe_gemm_bf16_tn(attn_in, L.wqkv, qkv, T, 3 * H, H, status, st));
-    PE_TRY(pe_rope_qk_inplace(qkv, position_ids, L.is_global ? model->rope_global : model->rope_local,
-                              model->max_positions, T, nh, status, st));
+    const void* rope_table = L.is_global ? model->rope_global : model->rope_local;
+    if (get_option(OPT_FUSED_ROPE)) {
+      PE_TRY(pe_gemm_qkv_rope_bf16(attn_in, L.wqkv, qkv, T, nh, H, position_ids, rope_table,
+                                   model->max_positions, status, st));
+    } else {
+      PE_TRY(pe_gemm_bf16_tn(attn_in, L.wqkv, qkv, T, 3 * H, H, status, st));
+      PE_TRY(pe_rope_qk_inplace(qkv, position_ids, rope_table, model->max_positions, T, nh, status, st));
+    }
     PE_TRY(attn_run(qkv, tiles, n_seqs, T, nh, L.is_global ? -1 : model->half_window, bm, ctx, status,
                     st));
     PE_TRY(pe_gemm_bf16_tn(ctx, L.wo, tmp, T, H, H, status, st));

@@ -41,11 +41,22 @@ __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
-template <bool GEGLU>
+enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2 };
+
+// Extra operands of the Wqkv + RoPE epilogue.
+struct RopeArgs {
+  const int64_t* pos;            // [M] position of each row
+  const __nv_bfloat16* table;    // [max_positions, 64]: cos of the 32 frequencies, then sin
+  int rope_cols;                 // columns [0, rope_cols) are q and k heads, the rest is v
+  int max_positions;
+};
+
+template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     __nv_bfloat16* __restrict__ C, int M, int n_out, int K, int gate_row0,
-                    int num_m, int num_n, int* status) {
+                    int num_m, int num_n, RopeArgs rope, int* status) {
+  constexpr bool GEGLU = MODE == GEMM_GEGLU;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = base + STAGES * STAGE_BYTES;
@@ -155,7 +166,58 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
-      if constexpr (!GEGLU) {
+      if constexpr (MODE == GEMM_QKV_ROPE) {
+        // One 64-column head at a time: rotate the (j, j + 32) pairs of q and k heads by the
+        // row's position, on values rounded to bf16 first (as the unfused path stores them).
+        const int col0 = nt * BN;
+        __nv_bfloat16* crow = C + size_t(row) * n_out + col0;
+        uint4 cs[8];  // cos[0..31] then sin[0..31] of this row's position, bf16
+        if (col0 < rope.rope_cols) {
+          int64_t p = row < M ? rope.pos[row] : 0;
+          if (p < 0 || p >= rope.max_positions) {
+            set_status(status, ST_BAD_POSITION);
+            p = 0;
+          }
+          const uint4* trow = reinterpret_cast<const uint4*>(rope.table + p * 64);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) cs[i] = __ldg(trow + i);
+        }
+#pragma unroll 1
+        for (int hp = 0; hp < BN / 64; ++hp) {
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32(t_addr + hp * 64, lo);
+          tmem_ld_32x32(t_addr + hp * 64 + 32, hi);
+          tmem_ld_wait();
+          const int col = col0 + hp * 64;
+          if (row < M && col + 64 <= n_out) {
+            if (col < rope.rope_cols) {
+              const __nv_bfloat16* cb = reinterpret_cast<const __nv_bfloat16*>(cs);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float ol, oh;
+                rope_pair(round_bf16(__uint_as_float(lo[i])), round_bf16(__uint_as_float(hi[i])),
+                          __bfloat162float(cb[i]), __bfloat162float(cb[32 + i]), ol, oh);
+                lo[i] = __float_as_uint(ol);
+                hi[i] = __float_as_uint(oh);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(lo[j * 8 + 0]), __uint_as_float(lo[j * 8 + 1]));
+              o.y = pack_bf16(__uint_as_float(lo[j * 8 + 2]), __uint_as_float(lo[j * 8 + 3]));
+              o.z = pack_bf16(__uint_as_float(lo[j * 8 + 4]), __uint_as_float(lo[j * 8 + 5]));
+              o.w = pack_bf16(__uint_as_float(lo[j * 8 + 6]), __uint_as_float(lo[j * 8 + 7]));
+              *reinterpret_cast<uint4*>(crow + hp * 64 + j * 8) = o;
+              o.x = pack_bf16(__uint_as_float(hi[j * 8 + 0]), __uint_as_float(hi[j * 8 + 1]));
+              o.y = pack_bf16(__uint_as_float(hi[j * 8 + 2]), __uint_as_float(hi[j * 8 + 3]));
+              o.z = pack_bf16(__uint_as_float(hi[j * 8 + 4]), __uint_as_float(hi[j * 8 + 5]));
+              o.w = pack_bf16(__uint_as_float(hi[j * 8 + 6]), __uint_as_float(hi[j * 8 + 7]));
+              *reinterpret_cast<uint4*>(crow + hp * 64 + 32 + j * 8) = o;
+            }
+          }
+        }
+      } else if constexpr (!GEGLU) {
         const int col0 = nt * BN;
         __nv_bfloat16* crow = C + size_t(row) * n_out + col0;
 #pragma unroll 1
@@ -227,14 +289,16 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-template <bool GEGLU>
+template <int MODE>
 static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_out, int K,
-                       int w_rows, int gate_row0, int32_t* status, cudaStream_t stream) {
-  static bool attr_set[2] = {false, false};
-  auto kern = gemm_bf16_tn_kernel<GEGLU>;
-  if (!attr_set[GEGLU ? 1 : 0]) {
+                       int w_rows, int gate_row0, RopeArgs rope, int32_t* status,
+                       cudaStream_t stream) {
+  constexpr bool GEGLU = MODE == GEMM_GEGLU;
+  static bool attr_set = false;  // one flag per instantiation
+  auto kern = gemm_bf16_tn_kernel<MODE>;
+  if (!attr_set) {
     PE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
-    attr_set[GEGLU ? 1 : 0] = true;
+    attr_set = true;
   }
   CUtensorMap tmA, tmB;
   int rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM);
@@ -248,7 +312,7 @@ static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_o
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, static_cast<__nv_bfloat16*>(C),
                                                   (int)M, n_out, K, gate_row0, num_m, num_n,
-                                                  status);
+                                                  rope, status);
   PE_LAUNCH_CHECK("gemm_bf16_tn_kernel");
   return PE_OK;
 }
@@ -271,8 +335,22 @@ extern "C" int pe_gemm_bf16_tn(const void* A, const void* W, void* C, int64_t M,
   if (M == 0) return PE_OK;
   int rc = pe::check_gemm_args(A, W, C, M, Nout, K, "pe_gemm_bf16_tn");
   if (rc != PE_OK) return rc;
-  return pe::launch_gemm<false>(A, W, C, M, Nout, K, Nout, 0, status,
-                                static_cast<cudaStream_t>(stream));
+  return pe::launch_gemm<pe::GEMM_PLAIN>(A, W, C, M, Nout, K, Nout, 0, pe::RopeArgs{}, status,
+                                         static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int pe_gemm_qkv_rope_bf16(const void* A, const void* Wqkv, void* qkv, int64_t M, int nh,
+                                     int K, const int64_t* position_ids, const void* table,
+                                     int max_positions, int32_t* status, void* stream) {
+  if (M == 0) return PE_OK;
+  PE_REQUIRE(nh > 0 && position_ids && table && max_positions > 0,
+             "pe_gemm_qkv_rope_bf16: bad RoPE arguments");
+  const int n_out = 3 * nh * 64;
+  int rc = pe::check_gemm_args(A, Wqkv, qkv, M, n_out, K, "pe_gemm_qkv_rope_bf16");
+  if (rc != PE_OK) return rc;
+  pe::RopeArgs rope{position_ids, static_cast<const __nv_bfloat16*>(table), 2 * nh * 64, max_positions};
+  return pe::launch_gemm<pe::GEMM_QKV_ROPE>(A, Wqkv, qkv, M, n_out, K, n_out, 0, rope, status,
+                                            static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int pe_gemm_geglu_bf16(const void* A, const void* Wi, void* out, int64_t M, int I, int K,
@@ -280,6 +358,6 @@ extern "C" int pe_gemm_geglu_bf16(const void* A, const void* Wi, void* out, int6
   if (M == 0) return PE_OK;
   int rc = pe::check_gemm_args(A, Wi, out, M, I, K, "pe_gemm_geglu_bf16");
   if (rc != PE_OK) return rc;
-  return pe::launch_gemm<true>(A, Wi, out, M, I, K, 2 * I, I, status,
-                               static_cast<cudaStream_t>(stream));
+  return pe::launch_gemm<pe::GEMM_GEGLU>(A, Wi, out, M, I, K, 2 * I, I, pe::RopeArgs{}, status,
+                                         static_cast<cudaStream_t>(stream));
 }

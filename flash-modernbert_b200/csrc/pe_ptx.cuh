@@ -191,6 +191,14 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// One RoPE pair (dims j and j + 32 of a head): explicit roundings so that every kernel
+// that rotates produces the same bits.
+__device__ __forceinline__ void rope_pair(float lo, float hi, float c, float s, float& out_lo,
+                                          float& out_hi) {
+  out_lo = __fmaf_rn(lo, c, -__fmul_rn(hi, s));
+  out_hi = __fmaf_rn(hi, c, __fmul_rn(lo, s));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -336,10 +336,7 @@ rope_qk_kernel(__nv_bfloat16* __restrict__ qkv, const int64_t* __restrict__ pos,
   unpack8(__ldg(reinterpret_cast<const uint4*>(trow + 32)), s);
   float olo[8], ohi[8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    olo[e] = lo[e] * c[e] - hi[e] * s[e];
-    ohi[e] = hi[e] * c[e] + lo[e] * s[e];
-  }
+  for (int e = 0; e < 8; ++e) rope_pair(lo[e], hi[e], c[e], s[e], olo[e], ohi[e]);
   *reinterpret_cast<uint4*>(base) = pack8(olo);
   *reinterpret_cast<uint4*>(base + 32) = pack8(ohi);
 }

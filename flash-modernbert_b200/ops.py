@@ -164,6 +164,22 @@ def rope_qk_inplace(qkv: Tensor, position_ids: Tensor, table: Tensor, n_heads: i
     return qkv
 
 
+def linear_qkv_rope(x: Tensor, wqkv: Tensor, position_ids: Tensor, table: Tensor, n_heads: int) -> Tensor:
+    """`rope_qk_inplace(_linear(x, wqkv), ...)` as one kernel: the rotation runs in the GEMM epilogue."""
+    x = _bf16_cuda(x, "x")
+    wqkv = _bf16_cuda(wqkv, "wqkv")
+    flat = x.reshape(-1, x.shape[-1])
+    out = torch.empty(flat.shape[0], 3 * n_heads * 64, dtype=torch.bfloat16, device=x.device)
+    with _Call(x) as c:
+        _lib.check(c.lib.pe_gemm_qkv_rope_bf16(flat.data_ptr(), wqkv.data_ptr(), out.data_ptr(),
+                                               flat.shape[0], n_heads, wqkv.shape[1],
+                                               position_ids.contiguous().data_ptr(),
+                                               _bf16_cuda(table, "table").data_ptr(), table.shape[0],
+                                               status_word(x.device).data_ptr(), c.stream),
+                   "pe_gemm_qkv_rope_bf16")
+    return out
+
+
 def attention_varlen_qkv(qkv: Tensor, cu_seqlens: Tensor, max_seqlen: int, n_heads: int,
                          half_window: int | None) -> Tensor:
     """Varlen attention on the fused, already-rotated `qkv [T, 3*n_heads*64]`;

@@ -76,6 +76,9 @@ int pe_device_check(void);
 /* Process-wide switch. key 1 (PE_OPT_FUSED_GEGLU, default 1): pe_forward_packed runs Wi and
  * GeGLU as one kernel (1) or as pe_gemm_bf16_tn followed by pe_geglu (0). */
 #define PE_OPT_FUSED_GEGLU 1
+/* key 2 (PE_OPT_FUSED_ROPE, default 1): Wqkv and RoPE as one kernel (1) or as pe_gemm_bf16_tn
+ * followed by pe_rope_qk_inplace (0). */
+#define PE_OPT_FUSED_ROPE 2
 int pe_set_option(int key, int value);
 
 /* ---- padding boundary ------------------------------------------------------ */
@@ -148,6 +151,14 @@ int pe_gemm_bf16_tn(const void* A, const void* W, void* C, int64_t M, int Nout, 
  * never written to memory. */
 int pe_gemm_geglu_bf16(const void* A, const void* Wi, void* out, int64_t M, int I, int K,
                        int32_t* status, void* stream);
+
+/* The Wqkv projection (packed_encoders/forward.py:191) and the RoPE that follows it
+ * (packed_encoders/ops.py:496) in one kernel: qkv = A Wqkv^T rounded to bf16, then the q and k
+ * heads rotated by table[position_ids[row]] in the epilogue; v columns are stored as they are.
+ * qkv: bf16 [M, 3*nh*64]. Same bits as pe_gemm_bf16_tn followed by pe_rope_qk_inplace. */
+int pe_gemm_qkv_rope_bf16(const void* A, const void* Wqkv, void* qkv, int64_t M, int nh, int K,
+                          const int64_t* position_ids, const void* table, int max_positions,
+                          int32_t* status, void* stream);
 
 /* ---- attention -------------------------------------------------------------- */
 

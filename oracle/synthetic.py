@@ -78,6 +78,9 @@ def workload(name: str, vocab: int = VOCAB, seed: int = 0) -> Workload:
     elif name == "cfg3":    # documents (headline): 512, lognormal(median 400, sigma .8) in [64, 8192]
         lengths = _lognormal(gen, 512, 400.0, 0.8, 64, 8192)
         arch = "base"
+    elif name == "cfg3q":   # every fourth document of cfg3: a profiling-sized slice of the headline workload
+        lengths = _lognormal(gen, 512, 400.0, 0.8, 64, 8192)[::4]
+        arch = "base"
     elif name == "cfg4":    # long documents on the large model: 64, U[2048, 8192]
         lengths = torch.randint(2048, 8193, (64,), generator=gen).tolist()
         arch = "large"

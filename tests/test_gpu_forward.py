@@ -57,7 +57,7 @@ def test_tiny_model_against_golden_and_oracle(pe, cuda_device, tiny_models):
     assert torch.equal(pe.packed_forward(gpu, params, ids, cu, max_s, pos), out)
 
 
-def test_fused_and_unfused_mlp_agree(pe, cuda_device, tiny_models):
+def test_fused_and_unfused_epilogues_agree(pe, cuda_device, tiny_models):
     from flash_modernbert_b200 import _lib
 
     _, _, gpu, vocab = tiny_models
@@ -68,9 +68,11 @@ def test_fused_and_unfused_mlp_agree(pe, cuda_device, tiny_models):
     try:
         fused = pe.packed_forward(gpu, params, *args)
         _lib.check(lib.pe_set_option(_lib.OPT_FUSED_GEGLU, 0), "pe_set_option")
+        _lib.check(lib.pe_set_option(_lib.OPT_FUSED_ROPE, 0), "pe_set_option")
         unfused = pe.packed_forward(gpu, params, *args)
     finally:
         lib.pe_set_option(_lib.OPT_FUSED_GEGLU, 1)
+        lib.pe_set_option(_lib.OPT_FUSED_ROPE, 1)
     assert torch.equal(fused, unfused)
 
 

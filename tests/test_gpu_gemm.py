@@ -78,3 +78,18 @@ def test_fused_wi_geglu_equals_two_kernels(pe, cuda_device, m, inter, k):
     assert torch.equal(fused, two)                 # same rounding points => same bits
     ref = O.geglu(O.linear(a, wi))
     assert float((fused.cpu().float() - ref).abs().max()) <= 0.02 * float(ref.abs().max()) + 1e-3
+
+
+@pytest.mark.parametrize("m,n_heads,k", [(129, 12, 768), (1000, 12, 768), (300, 16, 1024), (200, 28, 1792), (77, 4, 256)])
+def test_fused_wqkv_rope_equals_two_kernels(pe, cuda_device, m, n_heads, k):
+    from flash_modernbert_b200 import ops
+
+    a, w, a_d, w_d = _inputs(m, 3 * n_heads * 64, k, cuda_device, seed=3)
+    pos = torch.randint(0, 8192, (m,), generator=torch.Generator().manual_seed(m)).to(cuda_device)
+    table = ops.rope_table(10000.0, 8192, cuda_device)
+    fused = ops.linear_qkv_rope(a_d, w_d, pos, table, n_heads)
+    two = ops.rope_qk_inplace(ops._linear(a_d, w_d), pos, table, n_heads)
+    ops.check_status(cuda_device)
+    assert torch.equal(fused, two)                 # same rounding points => same bits
+    h = n_heads * 64
+    assert torch.equal(fused[:, 2 * h:], ops._linear(a_d, w_d)[:, 2 * h:])   # v is not rotated
