@@ -170,7 +170,7 @@ def launches_per_forward(model) -> int:
     n = 2  # embedding+LN, attention schedule
     for layer in model.layers:
         has_norm = not isinstance(layer.attn_norm, torch.nn.Identity)
-        n += (1 if has_norm else 0) + 7  # Wqkv, RoPE, attention, Wo, add+LN, Wi+GeGLU, Wo_mlp
+        n += (1 if has_norm else 0) + 6  # Wqkv+RoPE, attention, Wo, add+LN, Wi+GeGLU, Wo_mlp
     return n + 1  # final add+LN
 
 
@@ -186,8 +186,12 @@ def time_gemm_kernels(model, tokens: int, device, reps: int = 5) -> dict:
     gen = torch.Generator(device=device).manual_seed(0)
     xh = torch.randn(tokens, H, device=device, generator=gen).to(torch.bfloat16)
     xi = torch.randn(tokens, I, device=device, generator=gen).to(torch.bfloat16)
+    pos = torch.arange(tokens, device=device, dtype=torch.int64) % 512
+    table = ops.rope_table(10000.0, 8192, device)
+    nh = cfg.num_attention_heads
     shapes = {
-        "Wqkv": (lambda: ops._linear(xh, layer.attn.Wqkv.weight), 2.0 * tokens * 3 * H * H),
+        "Wqkv+RoPE": (lambda: ops.linear_qkv_rope(xh, layer.attn.Wqkv.weight, pos, table, nh),
+                      2.0 * tokens * 3 * H * H),
         "Wo": (lambda: ops._linear(xh, layer.attn.Wo.weight), 2.0 * tokens * H * H),
         "Wi+GeGLU": (lambda: ops.linear_geglu(xh, layer.mlp.Wi.weight), 2.0 * tokens * 2 * I * H),
         "Wo_mlp": (lambda: ops._linear(xi, layer.mlp.Wo.weight), 2.0 * tokens * I * H),

@@ -30,6 +30,7 @@ _ERR_NAMES = {
 }
 OPT_FUSED_GEGLU = 1
 OPT_FUSED_ROPE = 2
+OPT_LOCAL_ATTN_SINGLE_PASS = 3
 
 
 class NativeLibraryError(PackedEncodersError):

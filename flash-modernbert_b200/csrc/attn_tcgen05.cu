@@ -29,7 +29,8 @@ namespace pe {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BN = 128;
-constexpr int TC_STAGES = 3;
+constexpr int TC_STAGES = 4;
+constexpr int TC_PREFETCH_ITEMS = 3;  // how many items ahead the producer warms L2
 constexpr int TC_TILE_BYTES = 128 * 64 * 2;          // one 128 x 64 bf16 tile (Q, K or V)
 constexpr int TC_P_BYTES = 128 * 128 * 2;            // one P buffer: two 128 x 64 halves
 constexpr int TC_THREADS = 192;
@@ -42,13 +43,13 @@ constexpr uint32_t TC_O_COL = 256;  // O[b] at columns 256 + b * 64
 enum {
   TCB_Q_FULL = 0,     // 2
   TCB_Q_EMPTY = 2,    // 2
-  TCB_KV_FULL = 4,    // 3
-  TCB_KV_EMPTY = 7,   // 3
-  TCB_S_FULL = 10,    // 2
-  TCB_S_EMPTY = 12,   // 2
-  TCB_P_FULL = 14,    // 2
-  TCB_O_FULL = 16,    // 2
-  TCB_COUNT = 18
+  TCB_KV_FULL = 4,    // 4
+  TCB_KV_EMPTY = 8,   // 4
+  TCB_S_FULL = 12,    // 2
+  TCB_S_EMPTY = 14,   // 2
+  TCB_P_FULL = 16,    // 2
+  TCB_O_FULL = 18,    // 2
+  TCB_COUNT = 20
 };
 
 // One work item: a 128-query tile of one sequence, for one head.
@@ -99,6 +100,7 @@ __device__ __forceinline__ void tmem_ld_32x32_nowait(uint32_t taddr, uint32_t* v
       : "memory");
 }
 
+template <bool LOCAL>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __restrict__ tile_info,
                       const int32_t* __restrict__ total_tiles_ptr, int nh, int half_window,
@@ -156,6 +158,19 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         const TcItem it = tc_load_item(tile_info, item, nh, half_window);
         const int qcol = it.head * 64, kcol = H + qcol, vcol = 2 * H + qcol;
         const uint32_t qb = n & 1;
+        {  // warm L2 with the first tiles of an item a few steps ahead: its loads then miss no DRAM
+          const int ahead = item + TC_PREFETCH_ITEMS * stride_items;
+          if (ahead < total_items) {
+            const TcItem nx = tc_load_item(tile_info, ahead, nh, half_window);
+            const int c = nx.head * 64;
+            tma_prefetch_l2_2d(&tm_qkv, c, nx.seq_begin + nx.q0);
+            for (int j = 0; j < min(nx.n_kv, 2); ++j) {
+              const int r = nx.seq_begin + nx.kv_start + j * TC_BN;
+              tma_prefetch_l2_2d(&tm_qkv, H + c, r);
+              tma_prefetch_l2_2d(&tm_qkv, 2 * H + c, r);
+            }
+          }
+        }
         if (!mbar_wait(bar(TCB_Q_EMPTY + qb), ((n >> 1) & 1) ^ 1u, status, ST_ATTN_TIMEOUT)) break;
         mbar_expect_tx(bar(TCB_Q_FULL + qb), TC_TILE_BYTES);
         tma_load_2d(sQ + qb * TC_TILE_BYTES, &tm_qkv, bar(TCB_Q_FULL + qb), qcol, it.seq_begin + it.q0);
@@ -177,6 +192,61 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
   } else if (warp == 5) {
     // ---------------------------------------------------------------- MMA issuer
     if (elect_one()) {
+      if constexpr (LOCAL) {
+        // One item = at most two key tiles = one softmax pass.  S of item n goes to region
+        // n & 1 (256 columns) one item ahead of the softmax; O of item n is accumulated over its
+        // tiles into the first 64 columns of the same region once its P is complete.
+        constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0);
+        constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 64, 1);
+        uint32_t gq = 0, gp = 0, nq = 0, np = 0;
+        int q_item = blockIdx.x;
+        bool ok = true;
+        auto issue_qk_item = [&]() {
+          const TcItem it = tc_load_item(tile_info, q_item, nh, half_window);
+          const uint32_t r = nq & 1;
+          ok = mbar_wait(bar(TCB_S_EMPTY + r), ((nq >> 1) & 1) ^ 1u, status, ST_ATTN_MMA_TIMEOUT) &&
+               mbar_wait(bar(TCB_Q_FULL + r), (nq >> 1) & 1, status, ST_ATTN_MMA_TIMEOUT);
+          const uint64_t qdesc = umma_smem_desc_sw128(sQ + r * TC_TILE_BYTES, 1024);
+          for (int j = 0; ok && j < it.n_kv; ++j, ++gq) {
+            const uint32_t s = gq % TC_STAGES;
+            ok = mbar_wait(bar(TCB_KV_FULL + s), (gq / TC_STAGES) & 1, status, ST_ATTN_MMA_TIMEOUT);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t kdesc = umma_smem_desc_sw128(sKV + s * 2 * TC_TILE_BYTES, 1024);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_ss(tmem_base + r * 256 + j * 128, qdesc + 2u * kk, kdesc + 2u * kk, idesc_qk,
+                      kk != 0 ? 1u : 0u);
+          }
+          umma_commit(bar(TCB_S_FULL + r));
+          umma_commit(bar(TCB_Q_EMPTY + r));
+          ++nq;
+          q_item += stride_items;
+        };
+        if (q_item < total_items) issue_qk_item();
+        for (int p_item = blockIdx.x; ok && p_item < total_items; p_item += stride_items, ++np) {
+          if (q_item < total_items) issue_qk_item();  // next item's S while this item's softmax runs
+          if (!ok) break;
+          const TcItem it = tc_load_item(tile_info, p_item, nh, half_window);
+          const uint32_t r = np & 1;
+          if (!mbar_wait(bar(TCB_P_FULL), np & 1, status, ST_ATTN_MMA_TIMEOUT)) break;
+          tc_fence_after();
+          for (int j = 0; j < it.n_kv; ++j, ++gp) {
+            const uint32_t s = gp % TC_STAGES;
+            const uint32_t pbase = sP + j * TC_P_BYTES;
+            const uint32_t vbase = sKV + s * 2 * TC_TILE_BYTES + TC_TILE_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint64_t pdesc =
+                  umma_smem_desc_sw128(pbase + (kk >> 2) * TC_TILE_BYTES, 1024) + 2u * (kk & 3);
+              const uint64_t vdesc = umma_smem_desc_sw128(vbase + kk * 2048, 1024);
+              umma_ss(tmem_base + r * 256, pdesc, vdesc, idesc_pv, (j | kk) != 0 ? 1u : 0u);
+            }
+            umma_commit(bar(TCB_KV_EMPTY + s));
+          }
+          umma_commit(bar(TCB_O_FULL + r));
+        }
+      } else {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 64, 1);  // B (= V) is MN-major
       // Two cursors over the same flat sequence of key tiles: `q` issues S = Q K^T,
@@ -237,6 +307,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
           }
         }
       }
+      }
     }
     __syncwarp();
   } else {
@@ -246,6 +317,120 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
     const float scale_log2 = 0.125f * 1.4426950408889634f;
     uint32_t g = 0;  // key tiles consumed so far
     bool ok = true;
+    if constexpr (LOCAL) {
+      // Sliding-window layers (|i - j| <= 64): an item has at most two key tiles, both fully
+      // masked bands, so the whole item is one softmax pass.  Row r of the tile can only see
+      // columns [r, r + 128] of the 256 fetched keys; warp w therefore reads 32-column chunks
+      // w..3 of tile 0 and 0..w of tile 1 (five of eight) and writes zeros into the rest of P.
+      // S of the item sits in tensor-memory region n & 1 (256 columns); once every row is in
+      // registers, O = P V is accumulated into the first 64 columns of the same region.
+      int4 info = __ldg(tile_info + blockIdx.x / nh);
+      uint32_t n = 0;
+      for (int item = blockIdx.x; item < total_items; item += stride_items, ++n) {
+        const TcItem it = tc_make_item(info, item, nh, half_window);
+        if (item + stride_items < total_items) info = __ldg(tile_info + (item + stride_items) / nh);
+        const uint32_t r = n & 1;
+        const int qi = it.q0 + row;
+        const int key_lo = max(0, qi - half_window);
+        const int key_hi = qi < it.len ? min(it.len - 1, qi + half_window) : -1;
+        if (!mbar_wait(bar(TCB_S_FULL + r), (n >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) break;
+        tc_fence_after();
+        const int n0 = 4 - warp;                       // chunks taken from tile 0
+        const int n1 = it.n_kv > 1 ? warp + 1 : 0;     // chunks taken from tile 1
+        const uint32_t region = lane_addr + r * 256;
+        uint32_t sv[5][32];
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+          if (k < n0 + n1) {
+            const int tile = k < n0 ? 0 : 1;
+            const int chunk = k < n0 ? warp + k : k - n0;
+            tmem_ld_32x32_nowait(region + tile * 128 + chunk * 32, sv[k]);
+          }
+        }
+        tmem_ld_wait();
+        float mx = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+          if (k < n0 + n1) {
+            const int tile = k < n0 ? 0 : 1;
+            const int chunk = k < n0 ? warp + k : k - n0;
+            const int key0 = it.kv_start + tile * 128 + chunk * 32;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int key = key0 + e;
+              const float v = (key >= key_lo && key <= key_hi) ? __uint_as_float(sv[k][e]) : -INFINITY;
+              sv[k][e] = __float_as_uint(v);
+              mx = fmaxf(mx, v);
+            }
+          }
+        }
+        const float m_safe = (mx == -INFINITY) ? 0.f : mx * scale_log2;
+        float sum = 0.f;
+        const uint32_t prow = sP + row * 128;
+        const uint32_t sw = row & 7;
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+          if (k < n0 + n1) {
+            const int tile = k < n0 ? 0 : 1;
+            const int chunk = k < n0 ? warp + k : k - n0;
+            const uint32_t pbase = prow + tile * TC_P_BYTES + (chunk >> 1) * TC_TILE_BYTES;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float pv[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                pv[e] = ex2(fmaf(__uint_as_float(sv[k][i * 8 + e]), scale_log2, -m_safe));
+                sum += pv[e];
+              }
+              const uint32_t addr = pbase + (((((chunk & 1) << 2) + i) ^ sw) << 4);
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                           "r"(pack_bf16(pv[0], pv[1])), "r"(pack_bf16(pv[2], pv[3])),
+                           "r"(pack_bf16(pv[4], pv[5])), "r"(pack_bf16(pv[6], pv[7]))
+                           : "memory");
+            }
+          }
+        }
+        // zero the chunks this warp's rows cannot see: tile 0 chunks 0..w-1, tile 1 chunks w+1..3
+        for (int tile = 0; tile < it.n_kv; ++tile) {
+          const int c_begin = tile == 0 ? 0 : warp + 1;
+          const int c_end = tile == 0 ? warp : 4;
+          for (int chunk = c_begin; chunk < c_end; ++chunk) {
+            const uint32_t pbase = prow + tile * TC_P_BYTES + (chunk >> 1) * TC_TILE_BYTES;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t addr = pbase + (((((chunk & 1) << 2) + i) ^ sw) << 4);
+              asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bar(TCB_P_FULL));
+
+        if (!mbar_wait(bar(TCB_O_FULL + r), (n >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) break;
+        tc_fence_after();
+        uint32_t ov[64];
+        tmem_ld_32x32_nowait(region, ov);
+        tmem_ld_32x32_nowait(region + 32, ov + 32);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(TCB_S_EMPTY + r));  // region r may take the next S
+        if (qi < it.len) {
+          const float inv = sum > 0.f ? 1.f / sum : 0.f;
+          __nv_bfloat16* orow = out + (int64_t(it.seq_begin) + qi) * H + it.head * 64;
+#pragma unroll
+          for (int d8 = 0; d8 < 8; ++d8) {
+            uint4 w4;
+            w4.x = pack_bf16(__uint_as_float(ov[d8 * 8 + 0]) * inv, __uint_as_float(ov[d8 * 8 + 1]) * inv);
+            w4.y = pack_bf16(__uint_as_float(ov[d8 * 8 + 2]) * inv, __uint_as_float(ov[d8 * 8 + 3]) * inv);
+            w4.z = pack_bf16(__uint_as_float(ov[d8 * 8 + 4]) * inv, __uint_as_float(ov[d8 * 8 + 5]) * inv);
+            w4.w = pack_bf16(__uint_as_float(ov[d8 * 8 + 6]) * inv, __uint_as_float(ov[d8 * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + d8 * 8) = w4;
+          }
+        }
+      }
+    } else {
     int4 info = __ldg(tile_info + blockIdx.x / nh);
     for (int item = blockIdx.x; ok && item < total_items; item += stride_items) {
       const TcItem it = tc_make_item(info, item, nh, half_window);
@@ -365,6 +550,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         }
       }
     }
+    }
   }
 
   tc_fence_before();
@@ -379,8 +565,10 @@ int attn_run_tc(const void* qkv, const int4* tile_info, const int32_t* total_til
                 int64_t T, int nh, int half_window, void* out, int32_t* status, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
-    PE_CUDA(cudaFuncSetAttribute(attn_varlen_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 TC_SMEM));
+    PE_CUDA(cudaFuncSetAttribute(attn_varlen_tc_kernel<false>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
+    PE_CUDA(cudaFuncSetAttribute(attn_varlen_tc_kernel<true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
     attr_set = true;
   }
   CUtensorMap tm;
@@ -389,8 +577,13 @@ int attn_run_tc(const void* qkv, const int4* tile_info, const int32_t* total_til
   if (rc != PE_OK) return rc;
   const int64_t max_items = max_tiles * nh;
   const int grid = (int)(max_items < sm_count() ? max_items : sm_count());
-  attn_varlen_tc_kernel<<<grid, TC_THREADS, TC_SMEM, st>>>(
-      tm, tile_info, total_tiles, nh, half_window, static_cast<__nv_bfloat16*>(out), status);
+  // The single-pass kernel relies on the band being exactly one key tile wide.
+  if (half_window == TC_BN / 2 && get_option(OPT_LOCAL_ATTN_SINGLE_PASS))
+    attn_varlen_tc_kernel<true><<<grid, TC_THREADS, TC_SMEM, st>>>(
+        tm, tile_info, total_tiles, nh, half_window, static_cast<__nv_bfloat16*>(out), status);
+  else
+    attn_varlen_tc_kernel<false><<<grid, TC_THREADS, TC_SMEM, st>>>(
+        tm, tile_info, total_tiles, nh, half_window, static_cast<__nv_bfloat16*>(out), status);
   PE_LAUNCH_CHECK("attn_varlen_tc_kernel");
   return PE_OK;
 }

@@ -79,6 +79,9 @@ int pe_device_check(void);
 /* key 2 (PE_OPT_FUSED_ROPE, default 1): Wqkv and RoPE as one kernel (1) or as pe_gemm_bf16_tn
  * followed by pe_rope_qk_inplace (0). */
 #define PE_OPT_FUSED_ROPE 2
+/* key 3 (PE_OPT_LOCAL_ATTN_SINGLE_PASS, default 1): sliding-window layers of long batches use the
+ * one-pass tensor-memory kernel (1) or the generic online-softmax one (0). */
+#define PE_OPT_LOCAL_ATTN_SINGLE_PASS 3
 int pe_set_option(int key, int value);
 
 /* ---- padding boundary ------------------------------------------------------ */
