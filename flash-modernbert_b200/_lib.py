@@ -98,6 +98,8 @@ PROTOTYPES = {
     "pe_attn_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "pe_attn_varlen": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p,
                                c_void_p, c_size_t, c_void_p, c_void_p]),
+    "pe_attn_varlen_static": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p,
+                                      c_void_p, c_void_p]),
     "pe_forward_workspace_bytes": (c_size_t, [POINTER(PeModel), c_int64, c_int]),
     "pe_forward_packed": (c_int, [POINTER(PeModel), c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                   c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),

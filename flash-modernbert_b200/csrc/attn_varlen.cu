@@ -13,6 +13,7 @@
 // max_seqlen, which gives the short-query tiles that ~30-token sequences want
 // (one 32-row CTA covers a whole sequence) and 64-row tiles otherwise.
 #include <algorithm>
+#include <mutex>
 
 #include "pe_host.h"
 #include "pe_ptx.cuh"
@@ -378,7 +379,61 @@ int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh
   return PE_OK;
 }
 
+// ---- scratch that needs no allocation -------------------------------------------------
+// pe_attn_varlen_static keeps its tile table in this array instead of caller memory.  Every
+// GPU that loads the library carries the array from load until the process exits.
+constexpr int STATIC_MAX_SEQS = 4096;
+constexpr int64_t STATIC_MAX_TOKENS = 1 << 20;
+constexpr size_t STATIC_SCRATCH_BYTES =
+    ((size_t(STATIC_MAX_SEQS + 2) * sizeof(int32_t) + 15) & ~size_t(15)) +
+    size_t(STATIC_MAX_TOKENS / 16 + STATIC_MAX_SEQS + 1) * sizeof(int4);
+static __device__ __align__(256) unsigned char g_attn_static_scratch[STATIC_SCRATCH_BYTES];
+
+// Device address of the array on the current device.  In host code the symbol's name is only
+// a handle, so the address is asked of the runtime, once per device, with that device current.
+static int static_scratch_ptr(void** out) {
+  static std::mutex lock;
+  static void* ptrs[64] = {nullptr};
+  int dev = 0;
+  PE_CUDA(cudaGetDevice(&dev));
+  PE_REQUIRE(dev >= 0 && dev < 64, "pe_attn_varlen_static: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> guard(lock);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    PE_CUDA(cudaGetSymbolAddress(&p, g_attn_static_scratch));
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return PE_OK;
+}
+
 }  // namespace pe
+
+extern "C" int pe_attn_varlen_static(const void* qkv, const int32_t* cu_seqlens, int n_seqs, int64_t T,
+                                     int nh, int half_window, int max_seqlen, void* out,
+                                     int32_t* status, void* stream) {
+  using namespace pe;
+  PE_REQUIRE(qkv && cu_seqlens && out, "pe_attn_varlen_static: null pointer");
+  PE_REQUIRE(n_seqs > 0 && T >= 0 && nh > 0 && nh <= 65535 && max_seqlen > 0,
+             "pe_attn_varlen_static: bad sizes");
+  if (n_seqs > STATIC_MAX_SEQS || T > STATIC_MAX_TOKENS) {
+    set_last_error("pe_attn_varlen_static: %d sequences / %lld tokens exceed the built-in scratch "
+                   "(at most %d sequences and %lld tokens); use pe_attn_varlen with caller scratch",
+                   n_seqs, (long long)T, STATIC_MAX_SEQS, (long long)STATIC_MAX_TOKENS);
+    return PE_ERR_WORKSPACE;
+  }
+  if (T == 0) return PE_OK;
+  void* scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);
+  if (rc != PE_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int bm = attn_pick_bm(max_seqlen);
+  // The scheduling kernel rewrites every table entry this call reads, so nothing left by an
+  // earlier call is used and nothing has to be cleared first.
+  rc = attn_schedule(cu_seqlens, n_seqs, bm, scratch, st);
+  if (rc != PE_OK) return rc;
+  return attn_run(qkv, scratch, n_seqs, T, nh, half_window, bm, out, status, st);
+}
 
 extern "C" size_t pe_attn_workspace_bytes(int64_t T, int n_seqs) {
   if (T < 0 || n_seqs < 0) return 0;

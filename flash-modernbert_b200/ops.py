@@ -197,3 +197,23 @@ def attention_varlen_qkv(qkv: Tensor, cu_seqlens: Tensor, max_seqlen: int, n_hea
                                         status_word(qkv.device).data_ptr(), c.stream),
                    "pe_attn_varlen")
     return out
+
+
+def attention_varlen_qkv_static(qkv: Tensor, cu_seqlens: Tensor, max_seqlen: int, n_heads: int,
+                                half_window: int | None) -> Tensor:
+    """`attention_varlen_qkv` through the entry point that brings its own scratch: for callers
+    that cannot allocate device memory (a host process whose allocator owns the whole GPU, a
+    request path with a frozen memory budget). At most 4096 sequences and 1,048,576 tokens;
+    calls share one built-in table, so keep them on one stream. Only the output tensor is
+    created here, by the caller's own allocator."""
+    qkv = _bf16_cuda(qkv, "qkv")
+    total = qkv.shape[0]
+    out = torch.empty(total, n_heads * 64, dtype=torch.bfloat16, device=qkv.device)
+    with _Call(qkv) as c:
+        _lib.check(c.lib.pe_attn_varlen_static(qkv.data_ptr(), cu_seqlens.contiguous().data_ptr(),
+                                               cu_seqlens.numel() - 1, total, n_heads,
+                                               -1 if half_window is None else half_window,
+                                               int(max_seqlen), out.data_ptr(),
+                                               status_word(qkv.device).data_ptr(), c.stream),
+                   "pe_attn_varlen_static")
+    return out

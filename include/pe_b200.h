@@ -178,6 +178,20 @@ int pe_attn_varlen(const void* qkv, const int32_t* cu_seqlens, int n_seqs, int64
                    int half_window, int max_seqlen, void* out, void* workspace,
                    size_t workspace_bytes, int32_t* status, void* stream);
 
+/* pe_attn_varlen for callers that must not allocate device memory and have none to lend: a
+ * plug-in hosted by a process whose own allocator already holds the whole GPU, or a serving
+ * thread with a frozen memory budget that may not call cudaMalloc (which can stall the device)
+ * on its request path.  No counterpart in the reference.  The tile table lives in a 1.1 MB
+ * array inside the library (every GPU that loads the library holds it until exit), so the
+ * call takes no workspace and calls no allocator.  Limits: n_seqs <= 4096 and T <= 1,048,576,
+ * beyond which it returns PE_ERR_WORKSPACE.  The first call on each device looks the array's
+ * address up once; make that call outside any stream capture.  All calls share the one array:
+ * each call rebuilds the part it reads, so nothing needs clearing, but two calls whose kernels
+ * may overlap on the GPU (different streams) race on it - keep them on one stream. */
+int pe_attn_varlen_static(const void* qkv, const int32_t* cu_seqlens, int n_seqs, int64_t T,
+                          int nh, int half_window, int max_seqlen, void* out, int32_t* status,
+                          void* stream);
+
 /* ---- whole forward ---------------------------------------------------------- */
 
 /* Scratch bytes for pe_forward_packed at a capacity of T tokens and n_seqs sequences. */
