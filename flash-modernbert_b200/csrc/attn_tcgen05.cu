@@ -33,7 +33,7 @@ constexpr int TC_STAGES = 4;
 constexpr int TC_PREFETCH_ITEMS = 3;  // how many items ahead the producer warms L2
 constexpr int TC_TILE_BYTES = 128 * 64 * 2;          // one 128 x 64 bf16 tile (Q, K or V)
 constexpr int TC_P_BYTES = 128 * 128 * 2;            // one P buffer: two 128 x 64 halves
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 192;  // 4 softmax warps + producer + MMA
 constexpr int TC_SMEM = TC_TILE_BYTES * (2 + 2 * TC_STAGES) + 2 * TC_P_BYTES + 1024 + 256;
 constexpr uint32_t TC_TMEM_COLS = 512;
 constexpr uint32_t TC_S_COL = 0;    // S[b] at columns b * 128
@@ -117,6 +117,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
   auto bar = [&](int i) { return bar_base + 8u * i; };
   const uint32_t tmem_slot = bar_base + 8u * TCB_COUNT;
 
+  constexpr int NSW = 4;  // softmax warps; then one producer warp, one MMA warp
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int H = nh * 64;
@@ -127,8 +128,9 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
       mbar_init(bar(TCB_Q_FULL + b), 1);
       mbar_init(bar(TCB_Q_EMPTY + b), 1);
       mbar_init(bar(TCB_S_FULL + b), 1);
-      mbar_init(bar(TCB_S_EMPTY + b), 4);
-      mbar_init(bar(TCB_P_FULL + b), 128);
+      mbar_init(bar(TCB_S_EMPTY + b), NSW);
+      mbar_init(bar(TCB_P_FULL + b), NSW);  // one arrival per softmax warp: per-thread arrivals
+                                            // on one mbarrier serialise and cost microseconds
       mbar_init(bar(TCB_O_FULL + b), 1);
     }
     for (int s = 0; s < TC_STAGES; ++s) {
@@ -138,7 +140,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
     mbar_fence_init();
     tma_prefetch_desc(&tm_qkv);
   }
-  if (warp == 5) {
+  if (warp == NSW + 1) {
     tmem_alloc(tmem_slot, TC_TMEM_COLS);
     tmem_relinquish();
   }
@@ -148,7 +150,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
-  if (warp == 4) {
+  if (warp == NSW) {
     // ---------------------------------------------------------------- TMA producer
     if (elect_one()) {
       uint32_t g = 0;  // key tiles loaded so far (ring position)
@@ -189,7 +191,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == NSW + 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (elect_one()) {
       if constexpr (LOCAL) {
@@ -312,8 +314,9 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- softmax warps
-    const int row = warp * 32 + lane;       // query row in the tile == tensor-memory lane
-    const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16);
+    const int wq = warp & 3;                // tensor-memory lane quarter of this warp
+    const int row = wq * 32 + lane;         // query row in the tile == tensor-memory lane
+    const uint32_t lane_addr = tmem_base + (uint32_t(wq * 32) << 16);
     const float scale_log2 = 0.125f * 1.4426950408889634f;
     uint32_t g = 0;  // key tiles consumed so far
     bool ok = true;
@@ -348,7 +351,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
           }
         }
         tmem_ld_wait();
-        float mx = -INFINITY;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
 #pragma unroll
         for (int k = 0; k < 5; ++k) {
           if (k < n0 + n1) {
@@ -360,12 +363,13 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
               const int key = key0 + e;
               const float v = (key >= key_lo && key <= key_hi) ? __uint_as_float(sv[k][e]) : -INFINITY;
               sv[k][e] = __float_as_uint(v);
-              mx = fmaxf(mx, v);
+              mx4[e & 3] = fmaxf(mx4[e & 3], v);
             }
           }
         }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const float m_safe = (mx == -INFINITY) ? 0.f : mx * scale_log2;
-        float sum = 0.f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         const uint32_t prow = sP + row * 128;
         const uint32_t sw = row & 7;
 #pragma unroll
@@ -380,7 +384,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
 #pragma unroll
               for (int e = 0; e < 8; ++e) {
                 pv[e] = ex2(fmaf(__uint_as_float(sv[k][i * 8 + e]), scale_log2, -m_safe));
-                sum += pv[e];
+                sum4[e & 3] += pv[e];
               }
               const uint32_t addr = pbase + (((((chunk & 1) << 2) + i) ^ sw) << 4);
               asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
@@ -403,9 +407,11 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
             }
           }
         }
+        const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(bar(TCB_P_FULL));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(TCB_P_FULL));
 
         if (!mbar_wait(bar(TCB_O_FULL + r), (n >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) break;
         tc_fence_after();
@@ -470,22 +476,23 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         const int tile_key0 = it.kv_start + j * TC_BN;
         const int c_lo = key_lo - tile_key0, c_hi = key_hi - tile_key0;  // valid columns [c_lo, c_hi]
         const bool full = (c_lo <= 0) && (c_hi >= TC_BN - 1);
-        float mx = -INFINITY;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
         if (full) {
 #pragma unroll
-          for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+          for (int c = 0; c < 128; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
         } else {
 #pragma unroll
           for (int c = 0; c < 128; ++c) {
             const float v = (c >= c_lo && c <= c_hi) ? __uint_as_float(sv[c]) : -INFINITY;
             sv[c] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
+            mx4[c & 3] = fmaxf(mx4[c & 3], v);
           }
         }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const float m_new = fmaxf(m_run, mx * scale_log2);
         const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
         const float alpha = ex2(m_run - m_safe);
-        float sum = 0.f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         const uint32_t prow = sP + b * TC_P_BYTES + row * 128;
 #pragma unroll
         for (int c8 = 0; c8 < 16; ++c8) {  // 16 chunks of 8 keys = 16 bytes of bf16
@@ -493,7 +500,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             p[e] = ex2(fmaf(__uint_as_float(sv[c8 * 8 + e]), scale_log2, -m_safe));
-            sum += p[e];
+            sum4[e & 3] += p[e];
           }
           const uint32_t addr = prow + (c8 >> 3) * TC_TILE_BYTES + (((c8 & 7) ^ (row & 7)) << 4);
           asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
@@ -503,7 +510,8 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         }
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(bar(TCB_P_FULL + b));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(TCB_P_FULL + b));
 
         if (j > 0) {  // fold in the previous tile's P V, then move to the new running maximum
           const uint32_t pb = b ^ 1;
@@ -519,7 +527,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
 #pragma unroll
           for (int d = 0; d < 64; ++d) acc[d] = (acc[d] + __uint_as_float(ov[d])) * alpha;
         }
-        l_run = l_run * alpha + sum;
+        l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m_run = m_new;
       }
       if (!ok) break;
@@ -555,7 +563,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == NSW + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TC_TMEM_COLS);
   }

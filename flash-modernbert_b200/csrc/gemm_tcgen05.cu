@@ -31,7 +31,9 @@ constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GEMM_THREADS = 192;
-constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int OUT_STAGE_BYTES = 32 * 128;  // one warp's 32 rows x 64 bf16 columns
+constexpr int OUT_BYTES = 4 * 2 * OUT_STAGE_BYTES;  // four epilogue warps, double-buffered
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + OUT_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t TMEM_COLS = 512;
 
 __device__ __forceinline__ float gelu_erf(float a) {
@@ -54,12 +56,13 @@ struct RopeArgs {
 template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    __nv_bfloat16* __restrict__ C, int M, int n_out, int K, int gate_row0,
+                    const __grid_constant__ CUtensorMap tmC, int M, int n_out, int K, int gate_row0,
                     int num_m, int num_n, RopeArgs rope, int* status) {
   constexpr bool GEGLU = MODE == GEMM_GEGLU;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = base + STAGES * STAGE_BYTES;
+  const uint32_t out_base = base + STAGES * STAGE_BYTES;
+  const uint32_t bar_base = out_base + OUT_BYTES;
   // barrier slots (8 bytes each): full[0..3], empty[4..7], tmem_full[8..9], tmem_empty[10..11]
   auto bar = [&](int i) { return bar_base + 8u * i; };
   const uint32_t tmem_slot = bar_base + 8u * 12;
@@ -81,6 +84,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -157,20 +161,54 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     __syncwarp();
   } else {
+    // Epilogue: 64 accumulator columns at a time - tcgen05.ld, round (and transform) in
+    // registers, write the warp's 32 x 64 block into its own 128-byte-swizzled staging buffer,
+    // and let TMA store it.  Row-per-thread global stores would cost one cache line per lane
+    // per instruction; the TMA store keeps the load/store unit out of the way and clips rows
+    // and columns that fall outside C.
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    const uint32_t stage0 = out_base + q * 2 * OUT_STAGE_BYTES;
+    uint32_t ob = 0;  // staging buffer in use
+    auto emit64 = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int col, int row0) {
+      if (lane == 0) tma_store_wait_read<1>();  // the buffer used two stores ago is free again
+      __syncwarp();
+      const uint32_t dst = stage0 + ob * OUT_STAGE_BYTES + lane * 128;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + ((j ^ (lane & 7)) << 4)),
+                     "r"(pack_bf16(__uint_as_float(lo[j * 8 + 0]), __uint_as_float(lo[j * 8 + 1]))),
+                     "r"(pack_bf16(__uint_as_float(lo[j * 8 + 2]), __uint_as_float(lo[j * 8 + 3]))),
+                     "r"(pack_bf16(__uint_as_float(lo[j * 8 + 4]), __uint_as_float(lo[j * 8 + 5]))),
+                     "r"(pack_bf16(__uint_as_float(lo[j * 8 + 6]), __uint_as_float(lo[j * 8 + 7])))
+                     : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (((4 + j) ^ (lane & 7)) << 4)),
+                     "r"(pack_bf16(__uint_as_float(hi[j * 8 + 0]), __uint_as_float(hi[j * 8 + 1]))),
+                     "r"(pack_bf16(__uint_as_float(hi[j * 8 + 2]), __uint_as_float(hi[j * 8 + 3]))),
+                     "r"(pack_bf16(__uint_as_float(hi[j * 8 + 4]), __uint_as_float(hi[j * 8 + 5]))),
+                     "r"(pack_bf16(__uint_as_float(hi[j * 8 + 6]), __uint_as_float(hi[j * 8 + 7])))
+                     : "memory");
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&tmC, stage0 + ob * OUT_STAGE_BYTES, col, row0);
+        tma_store_commit();
+      }
+      ob ^= 1u;
+    };
     uint32_t acc = 0, acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int m0 = (tile / num_n) * BM;
       const int nt = tile % num_n;
       if (!mbar_wait(bar(8 + acc), acc_phase, status, ST_GEMM_EPILOGUE_TIMEOUT)) break;
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
+      const int row0 = m0 + q * 32;
+      const int row = row0 + lane;
       const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
       if constexpr (MODE == GEMM_QKV_ROPE) {
         // One 64-column head at a time: rotate the (j, j + 32) pairs of q and k heads by the
         // row's position, on values rounded to bf16 first (as the unfused path stores them).
         const int col0 = nt * BN;
-        __nv_bfloat16* crow = C + size_t(row) * n_out + col0;
         uint4 cs[8];  // cos[0..31] then sin[0..31] of this row's position, bf16
         if (col0 < rope.rope_cols) {
           int64_t p = row < M ? rope.pos[row] : 0;
@@ -184,92 +222,58 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
 #pragma unroll 1
         for (int hp = 0; hp < BN / 64; ++hp) {
+          const int col = col0 + hp * 64;
+          if (col >= n_out) break;
           uint32_t lo[32], hi[32];
           tmem_ld_32x32(t_addr + hp * 64, lo);
           tmem_ld_32x32(t_addr + hp * 64 + 32, hi);
           tmem_ld_wait();
-          const int col = col0 + hp * 64;
-          if (row < M && col + 64 <= n_out) {
-            if (col < rope.rope_cols) {
-              const __nv_bfloat16* cb = reinterpret_cast<const __nv_bfloat16*>(cs);
+          if (col < rope.rope_cols) {
+            const __nv_bfloat16* cb = reinterpret_cast<const __nv_bfloat16*>(cs);
 #pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                float ol, oh;
-                rope_pair(round_bf16(__uint_as_float(lo[i])), round_bf16(__uint_as_float(hi[i])),
-                          __bfloat162float(cb[i]), __bfloat162float(cb[32 + i]), ol, oh);
-                lo[i] = __float_as_uint(ol);
-                hi[i] = __float_as_uint(oh);
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 o;
-              o.x = pack_bf16(__uint_as_float(lo[j * 8 + 0]), __uint_as_float(lo[j * 8 + 1]));
-              o.y = pack_bf16(__uint_as_float(lo[j * 8 + 2]), __uint_as_float(lo[j * 8 + 3]));
-              o.z = pack_bf16(__uint_as_float(lo[j * 8 + 4]), __uint_as_float(lo[j * 8 + 5]));
-              o.w = pack_bf16(__uint_as_float(lo[j * 8 + 6]), __uint_as_float(lo[j * 8 + 7]));
-              *reinterpret_cast<uint4*>(crow + hp * 64 + j * 8) = o;
-              o.x = pack_bf16(__uint_as_float(hi[j * 8 + 0]), __uint_as_float(hi[j * 8 + 1]));
-              o.y = pack_bf16(__uint_as_float(hi[j * 8 + 2]), __uint_as_float(hi[j * 8 + 3]));
-              o.z = pack_bf16(__uint_as_float(hi[j * 8 + 4]), __uint_as_float(hi[j * 8 + 5]));
-              o.w = pack_bf16(__uint_as_float(hi[j * 8 + 6]), __uint_as_float(hi[j * 8 + 7]));
-              *reinterpret_cast<uint4*>(crow + hp * 64 + 32 + j * 8) = o;
+            for (int i = 0; i < 32; ++i) {
+              float ol, oh;
+              rope_pair(round_bf16(__uint_as_float(lo[i])), round_bf16(__uint_as_float(hi[i])),
+                        __bfloat162float(cb[i]), __bfloat162float(cb[32 + i]), ol, oh);
+              lo[i] = __float_as_uint(ol);
+              hi[i] = __float_as_uint(oh);
             }
           }
+          emit64(lo, hi, col, row0);
         }
       } else if constexpr (!GEGLU) {
         const int col0 = nt * BN;
-        __nv_bfloat16* crow = C + size_t(row) * n_out + col0;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_addr + c * 32, v);
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col = col0 + c * 64;
+          if (col >= n_out) break;
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32(t_addr + c * 64, lo);
+          tmem_ld_32x32(t_addr + c * 64 + 32, hi);
           tmem_ld_wait();
-          if (row < M) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int col = col0 + c * 32 + j * 8;
-              if (col + 8 <= n_out) {
-                uint4 o;
-                o.x = pack_bf16(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
-                o.y = pack_bf16(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
-                o.z = pack_bf16(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
-                o.w = pack_bf16(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
-                *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) = o;
-              }
-            }
-          }
+          emit64(lo, hi, col, row0);
         }
       } else {
         const int col0 = nt * 128;
-        __nv_bfloat16* crow = C + size_t(row) * n_out + col0;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t va[32], vg[32];
-          tmem_ld_32x32(t_addr + c * 32, va);
-          tmem_ld_32x32(t_addr + 128 + c * 32, vg);
-          tmem_ld_wait();
-          if (row < M) {
+        for (int c = 0; c < 2; ++c) {
+          const int col = col0 + c * 64;
+          if (col >= n_out) break;
+          uint32_t lo[32], hi[32];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int col = col0 + c * 32 + j * 8;
-              if (col + 8 <= n_out) {
-                float r[8];
+          for (int h = 0; h < 2; ++h) {
+            uint32_t va[32], vg[32];
+            tmem_ld_32x32(t_addr + c * 64 + h * 32, va);
+            tmem_ld_32x32(t_addr + 128 + c * 64 + h * 32, vg);
+            tmem_ld_wait();
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  const float a = round_bf16(__uint_as_float(va[j * 8 + e]));
-                  const float g = round_bf16(__uint_as_float(vg[j * 8 + e]));
-                  r[e] = gelu_erf(a) * g;
-                }
-                uint4 o;
-                o.x = pack_bf16(r[0], r[1]);
-                o.y = pack_bf16(r[2], r[3]);
-                o.z = pack_bf16(r[4], r[5]);
-                o.w = pack_bf16(r[6], r[7]);
-                *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) = o;
-              }
+            for (int e = 0; e < 32; ++e) {
+              const float a = round_bf16(__uint_as_float(va[e]));
+              const float g = round_bf16(__uint_as_float(vg[e]));
+              (h == 0 ? lo : hi)[e] = __float_as_uint(gelu_erf(a) * g);
             }
           }
+          emit64(lo, hi, col, row0);
         }
       }
       tc_fence_before();
@@ -278,6 +282,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (lane == 0) tma_store_wait_all<0>();  // staging memory must outlive the stores that read it
+    __syncwarp();
   }
 
   // Common exit: every role arrives here (each of its waits is bounded).
@@ -305,12 +311,15 @@ static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_o
   if (rc != PE_OK) return rc;
   rc = make_tmap_bf16_2d(&tmB, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)K, 128);
   if (rc != PE_OK) return rc;
+  CUtensorMap tmC;  // output, stored in 32-row x 64-column boxes
+  rc = make_tmap_bf16_2d(&tmC, C, (uint64_t)M, (uint64_t)n_out, (uint64_t)n_out, 32);
+  if (rc != PE_OK) return rc;
   const int num_m = int((M + BM - 1) / BM);
   const int cols_per_tile = GEGLU ? 128 : BN;
   const int num_n = (n_out + cols_per_tile - 1) / cols_per_tile;
   const long long tiles = (long long)num_m * num_n;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, static_cast<__nv_bfloat16*>(C),
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, tmC,
                                                   (int)M, n_out, K, gate_row0, num_m, num_n,
                                                   rope, status);
   PE_LAUNCH_CHECK("gemm_bf16_tn_kernel");

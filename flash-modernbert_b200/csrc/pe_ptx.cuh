@@ -65,20 +65,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: gives up after about one second of wall time (and never after
-// more than 2^26 polls), records `code` in the status word and returns false so
-// that the caller can unwind.
+// Bounded wait: polls until the phase completes or about a second has passed on the SM's
+// own cycle counter (cheap to read, unlike the global nanosecond timer), then records
+// `code` in the status word and returns false so that the caller can unwind.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (uint32_t it = 1; it < (1u << 26); ++it) {
+  const long long t0 = clock64();
+  for (uint32_t it = 1; it < (1u << 28); ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255u) == 0 && global_timer_ns() - t0 > 1000000000ull) break;
+    if ((it & 1023u) == 0 && clock64() - t0 > 2000000000ll) break;
   }
   set_status(status, code);
   return false;
@@ -116,6 +111,26 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int c0,
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1)
                : "memory");
+}
+
+// 2-D tiled store shared -> global (rows/columns outside the tensor are clipped), tracked by
+// the issuing thread's bulk async-group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Waits until at most N of this thread's store groups still have to read their shared memory.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ---- tensor memory ------------------------------------------------------------
