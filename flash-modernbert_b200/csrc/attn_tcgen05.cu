@@ -352,18 +352,41 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         }
         tmem_ld_wait();
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
+        // Interior item: all 256 fetched keys and all 128 query rows lie inside the sequence, so
+        // the band alone decides.  Then only the warp's first chunk (keys >= row: column e >= lane)
+        // and last chunk (keys <= row + 128: column e <= lane) need a per-element test.
+        const bool interior = it.kv_start >= 0 && it.kv_start + 2 * TC_BN <= it.len;
+        if (interior) {
 #pragma unroll
-        for (int k = 0; k < 5; ++k) {
-          if (k < n0 + n1) {
-            const int tile = k < n0 ? 0 : 1;
-            const int chunk = k < n0 ? warp + k : k - n0;
-            const int key0 = it.kv_start + tile * 128 + chunk * 32;
+          for (int k = 0; k < 5; ++k) {
+            if (k == 0 || k == 4) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const int key = key0 + e;
-              const float v = (key >= key_lo && key <= key_hi) ? __uint_as_float(sv[k][e]) : -INFINITY;
-              sv[k][e] = __float_as_uint(v);
-              mx4[e & 3] = fmaxf(mx4[e & 3], v);
+              for (int e = 0; e < 32; ++e) {
+                const bool ok_e = (k == 0) ? (e >= lane) : (e <= lane);
+                const float v = ok_e ? __uint_as_float(sv[k][e]) : -INFINITY;
+                sv[k][e] = __float_as_uint(v);
+                mx4[e & 3] = fmaxf(mx4[e & 3], v);
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; e += 2)
+                mx4[(e >> 1) & 3] = fmax3(mx4[(e >> 1) & 3], __uint_as_float(sv[k][e]), __uint_as_float(sv[k][e + 1]));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 5; ++k) {
+            if (k < n0 + n1) {
+              const int tile = k < n0 ? 0 : 1;
+              const int chunk = k < n0 ? warp + k : k - n0;
+              const int key0 = it.kv_start + tile * 128 + chunk * 32;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const int key = key0 + e;
+                const float v = (key >= key_lo && key <= key_hi) ? __uint_as_float(sv[k][e]) : -INFINITY;
+                sv[k][e] = __float_as_uint(v);
+                mx4[e & 3] = fmaxf(mx4[e & 3], v);
+              }
             }
           }
         }
@@ -479,7 +502,8 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
         if (full) {
 #pragma unroll
-          for (int c = 0; c < 128; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
+          for (int c = 0; c < 128; c += 2)
+            mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
         } else {
 #pragma unroll
           for (int c = 0; c < 128; ++c) {
@@ -524,8 +548,13 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
           tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64, ov);
           tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64 + 32, ov + 32);
           tmem_ld_wait();
+          if (__all_sync(0xffffffffu, alpha == 1.0f)) {  // common once the row maxima have settled
 #pragma unroll
-          for (int d = 0; d < 64; ++d) acc[d] = (acc[d] + __uint_as_float(ov[d])) * alpha;
+            for (int d = 0; d < 64; ++d) acc[d] += __uint_as_float(ov[d]);
+          } else {
+#pragma unroll
+            for (int d = 0; d < 64; ++d) acc[d] = (acc[d] + __uint_as_float(ov[d])) * alpha;
+          }
         }
         l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m_run = m_new;

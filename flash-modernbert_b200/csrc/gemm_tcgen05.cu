@@ -36,9 +36,6 @@ constexpr int OUT_BYTES = 4 * 2 * OUT_STAGE_BYTES;  // four epilogue warps, doub
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + OUT_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t TMEM_COLS = 512;
 
-__device__ __forceinline__ float gelu_erf(float a) {
-  return a * 0.5f * (1.0f + erff(a * 0.70710678118654752440f));
-}
 __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }

@@ -359,7 +359,7 @@ geglu_kernel(const __nv_bfloat16* __restrict__ proj, int64_t T, int I,
     unpack8(ld_stream(row + vec_per_row + c), g);
 #pragma unroll
     for (int e = 0; e < 8; ++e)
-      o[e] = a[e] * 0.5f * (1.0f + erff(a[e] * 0.70710678118654752440f)) * g[e];
+      o[e] = gelu_erf(a[e]) * g[e];
     reinterpret_cast<uint4*>(out)[i] = pack8(o);
   }
 }

@@ -267,3 +267,62 @@ def test_against_reference_gpu_packed_forward(pe, cuda_device, base_models):
         assert rep["min_token_cos"] >= COS_GATE, rep
     finally:
         sys.path.remove(str(ref_dir))
+
+
+def _subset(wl, picks):
+    seqs = wl.sequences()
+    return [seqs[i] for i in picks]
+
+
+@pytest.mark.parametrize("arch,config,picks", [
+    ("large", "cfg4", [5, 40]),          # two long documents (2,048..8,192 tokens) on ModernBERT-large
+    ("1b", "cfg5", [3, 100, 9000]),      # two queries and one document on the 1B-class model
+])
+def test_other_architectures_against_hf_eager(pe, cuda_device, arch, config, picks):
+    """cfg4 / cfg5 architectures (hidden 1024 / 1792, 28 layers, intermediate 2624 / 3840): a
+    seeded subset of the config's sequences, packed on the GPU against HF eager fp32 on the host."""
+    from flash_modernbert_b200 import forward
+
+    wl = S.workload(config)
+    seqs = _subset(wl, picks)
+    seqs = [s[:2000] for s in seqs]       # bound the CPU side of the check
+    cpu = S.make_model(arch)
+    gpu = S.make_model(arch, dtype=torch.bfloat16, device=cuda_device)
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    batch = pe.pack_sequences(seqs, device=cuda_device)
+    out = pe.packed_forward(gpu, params, *batch.forward_args())
+    forward.get_binding(gpu, params).check(sync=True)
+    ref = O.hf_eager_packed(cpu, seqs)
+    rep = O.cosine_report(out.cpu(), ref)
+    print(f"{config} subset on {arch}: {rep}")
+    assert rep["min_token_cos"] >= COS_GATE, rep
+    del gpu, cpu
+    torch.cuda.empty_cache()
+
+
+def test_cfg2_queries_through_token_bucket_graphs(pe, cuda_device, base_models):
+    """cfg2 (1,024 queries of 8..48 tokens, 28,671 tokens) in batches of 256 sequences: graph
+    replays equal the eager forward bit for bit and a handful of graphs serves all batches."""
+    from flash_modernbert_b200 import forward
+
+    cpu, gpu = base_models
+    wl = S.workload("cfg2")
+    seqs = wl.sequences()
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    pe.pack(gpu, validate=False, cuda_graph=pe.GraphConfig(pad_to=4096, max_batch=256, max_seq=64))
+    try:
+        runner = pe.get_state(gpu).packed_graph_runner
+        with torch.no_grad():
+            for start in range(0, len(seqs), 256):
+                batch = pe.pack_sequences(seqs[start:start + 256], device=cuda_device)
+                graphed = pe.packed_forward(gpu, params, *batch.forward_args())
+                with pe.no_cuda_graph(gpu):
+                    eager = pe.packed_forward(gpu, params, *batch.forward_args())
+                assert torch.equal(graphed, eager)
+        forward.get_binding(gpu, params).check(sync=True)
+        assert runner.replays == 4 and runner.captures == 1    # four ragged batches, one graph
+        ref = O.hf_eager_packed(cpu, seqs[768:776])
+        got = graphed[: sum(s.numel() for s in seqs[768:776])]
+        assert O.cosine_report(got.cpu(), ref)["min_token_cos"] >= COS_GATE
+    finally:
+        pe.unpack(gpu)
