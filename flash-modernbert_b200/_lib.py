@@ -31,6 +31,7 @@ _ERR_NAMES = {
 OPT_FUSED_GEGLU = 1
 OPT_FUSED_ROPE = 2
 OPT_LOCAL_ATTN_SINGLE_PASS = 3
+OPT_FUSED_RESIDUAL = 4
 
 
 class NativeLibraryError(PackedEncodersError):
@@ -95,6 +96,8 @@ PROTOTYPES = {
                                    c_void_p]),
     "pe_gemm_qkv_rope_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
                                       c_void_p, c_int, c_void_p, c_void_p]),
+    "pe_gemm_residual_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                      c_void_p, c_void_p]),
     "pe_attn_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "pe_attn_varlen": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p,
                                c_void_p, c_size_t, c_void_p, c_void_p]),

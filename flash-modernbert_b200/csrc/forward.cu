@@ -7,7 +7,7 @@
 namespace pe {
 
 static int g_options[OPT_COUNT] = {0, /*OPT_FUSED_GEGLU*/ 1, /*OPT_FUSED_ROPE*/ 1,
-                                   /*OPT_LOCAL_ATTN_SINGLE_PASS*/ 1};
+                                   /*OPT_LOCAL_ATTN_SINGLE_PASS*/ 1, /*OPT_FUSED_RESIDUAL*/ 1};
 
 int get_option(int key) { return (key > 0 && key < OPT_COUNT) ? g_options[key] : 0; }
 
@@ -115,6 +115,7 @@ extern "C" int pe_forward_packed(const pe_model* model, const int64_t* ids,
   const int bm = attn_pick_bm(max_seqlen);
   PE_TRY(attn_schedule(cu_seqlens, n_seqs, bm, tiles, st));
 
+  const bool fuse_res = get_option(OPT_FUSED_RESIDUAL) != 0;
   bool pending = false;  // tmp holds the previous layer's MLP output, not yet added to x
   for (int l = 0; l < model->n_layers; ++l) {
     const pe_layer_weights& L = model->layers[l];
@@ -126,6 +127,7 @@ extern "C" int pe_forward_packed(const pe_model* model, const int64_t* ids,
       if (pending) PE_TRY(pe_add_ln(x, tmp, nullptr, eps, T, H, x, nullptr, st));
       attn_in = x;
     }
+    pending = false;
     const void* rope_table = L.is_global ? model->rope_global : model->rope_local;
     if (get_option(OPT_FUSED_ROPE)) {
       PE_TRY(pe_gemm_qkv_rope_bf16(attn_in, L.wqkv, qkv, T, nh, H, position_ids, rope_table,
@@ -136,16 +138,25 @@ extern "C" int pe_forward_packed(const pe_model* model, const int64_t* ids,
     }
     PE_TRY(attn_run(qkv, tiles, n_seqs, T, nh, L.is_global ? -1 : model->half_window, bm, ctx, status,
                     st));
-    PE_TRY(pe_gemm_bf16_tn(ctx, L.wo, tmp, T, H, H, status, st));
-    PE_TRY(pe_add_ln(x, tmp, L.mlp_norm_w, eps, T, H, x, normed, st));
+    if (fuse_res) {  // x += Wo ctx in the GEMM epilogue, then a plain LayerNorm
+      PE_TRY(pe_gemm_residual_bf16(ctx, L.wo, x, x, T, H, H, status, st));
+      PE_TRY(pe_add_ln(x, nullptr, L.mlp_norm_w, eps, T, H, nullptr, normed, st));
+    } else {
+      PE_TRY(pe_gemm_bf16_tn(ctx, L.wo, tmp, T, H, H, status, st));
+      PE_TRY(pe_add_ln(x, tmp, L.mlp_norm_w, eps, T, H, x, normed, st));
+    }
     if (get_option(OPT_FUSED_GEGLU)) {
       PE_TRY(pe_gemm_geglu_bf16(normed, L.wi, act, T, I, H, status, st));
     } else {
       PE_TRY(pe_gemm_bf16_tn(normed, L.wi, proj, T, 2 * I, H, status, st));
       PE_TRY(pe_geglu(proj, T, I, act, st));
     }
-    PE_TRY(pe_gemm_bf16_tn(act, L.wo_mlp, tmp, T, H, I, status, st));
-    pending = true;
+    if (fuse_res) {  // the MLP residual lands in x right away instead of waiting for the next norm
+      PE_TRY(pe_gemm_residual_bf16(act, L.wo_mlp, x, x, T, H, I, status, st));
+    } else {
+      PE_TRY(pe_gemm_bf16_tn(act, L.wo_mlp, tmp, T, H, I, status, st));
+      pending = true;
+    }
   }
   PE_TRY(pe_add_ln(x, pending ? tmp : nullptr, model->final_norm_w, eps, T, H, nullptr, out, st));
 #undef PE_TRY

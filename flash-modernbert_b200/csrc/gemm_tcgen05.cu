@@ -40,10 +40,11 @@ __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
-enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2 };
+enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2, GEMM_RESIDUAL = 3 };
 
-// Extra operands of the Wqkv + RoPE epilogue.
+// Extra operands of the Wqkv + RoPE epilogue and of the residual epilogue.
 struct RopeArgs {
+  const __nv_bfloat16* residual; // [M, n_out] added to the rounded product (GEMM_RESIDUAL); may alias C
   const int64_t* pos;            // [M] position of each row
   const __nv_bfloat16* table;    // [max_positions, 64]: cos of the 32 frequencies, then sin
   int rope_cols;                 // columns [0, rope_cols) are q and k heads, the rest is v
@@ -238,6 +239,75 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           emit64(lo, hi, col, row0);
         }
+      } else if constexpr (MODE == GEMM_RESIDUAL) {
+        // C = bf16(X + bf16(acc)).  The warp fetches its 32 x 64 block of X coalesced (four rows
+        // per instruction), one block ahead of the accumulator it belongs to, turns it into
+        // row-per-thread form through the staging buffer, adds, and stores the sum from the
+        // same buffer.  X may be C: every block is read before the same warp overwrites it.
+        const int col0 = nt * BN;
+        auto fetch = [&](uint4 (&xr)[8], int col) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = row0 + i * 4 + (lane >> 3);
+            const int cc = col + (lane & 7) * 8;
+            xr[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (r < M && cc + 8 <= n_out)
+              xr[i] = *reinterpret_cast<const uint4*>(rope.residual + size_t(r) * n_out + cc);
+          }
+        };
+        uint4 xr[2][8];
+        fetch(xr[0], col0);
+#pragma unroll
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col = col0 + c * 64;
+          if (col >= n_out) break;
+          if (c + 1 < BN / 64) fetch(xr[(c + 1) & 1], col + 64);
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32(t_addr + c * 64, lo);
+          tmem_ld_32x32(t_addr + c * 64 + 32, hi);
+          tmem_ld_wait();
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          const uint32_t buf = stage0 + ob * OUT_STAGE_BYTES;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3);
+            const uint4 v = xr[c & 1][i];
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(
+                             buf + r * 128 + (((lane & 7) ^ (r & 7)) << 4)),
+                         "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                         : "memory");
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t addr = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
+            uint4 xv;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(xv.x), "=r"(xv.y), "=r"(xv.z), "=r"(xv.w)
+                         : "r"(addr));
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 xf = __bfloat1622float2(xp[e]);
+              const uint32_t* src = j < 4 ? lo : hi;
+              const float a0 = round_bf16(__uint_as_float(src[(j & 3) * 8 + 2 * e]));
+              const float a1 = round_bf16(__uint_as_float(src[(j & 3) * 8 + 2 * e + 1]));
+              o[e] = pack_bf16(xf.x + a0, xf.y + a1);
+            }
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]),
+                         "r"(o[2]), "r"(o[3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, buf, col, row0);
+            tma_store_commit();
+          }
+          ob ^= 1u;
+        }
       } else if constexpr (!GEGLU) {
         const int col0 = nt * BN;
 #pragma unroll 1
@@ -354,7 +424,8 @@ extern "C" int pe_gemm_qkv_rope_bf16(const void* A, const void* Wqkv, void* qkv,
   const int n_out = 3 * nh * 64;
   int rc = pe::check_gemm_args(A, Wqkv, qkv, M, n_out, K, "pe_gemm_qkv_rope_bf16");
   if (rc != PE_OK) return rc;
-  pe::RopeArgs rope{position_ids, static_cast<const __nv_bfloat16*>(table), 2 * nh * 64, max_positions};
+  pe::RopeArgs rope{nullptr, position_ids, static_cast<const __nv_bfloat16*>(table), 2 * nh * 64,
+                    max_positions};
   return pe::launch_gemm<pe::GEMM_QKV_ROPE>(A, Wqkv, qkv, M, n_out, K, n_out, 0, rope, status,
                                             static_cast<cudaStream_t>(stream));
 }
@@ -366,4 +437,16 @@ extern "C" int pe_gemm_geglu_bf16(const void* A, const void* Wi, void* out, int6
   if (rc != PE_OK) return rc;
   return pe::launch_gemm<pe::GEMM_GEGLU>(A, Wi, out, M, I, K, 2 * I, I, pe::RopeArgs{}, status,
                                          static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int pe_gemm_residual_bf16(const void* A, const void* W, const void* X, void* C, int64_t M,
+                                     int Nout, int K, int32_t* status, void* stream) {
+  if (M == 0) return PE_OK;
+  int rc = pe::check_gemm_args(A, W, C, M, Nout, K, "pe_gemm_residual_bf16");
+  if (rc != PE_OK) return rc;
+  PE_REQUIRE(X != nullptr && ((uintptr_t)X & 15) == 0, "pe_gemm_residual_bf16: X is NULL or unaligned");
+  pe::RopeArgs args{};
+  args.residual = static_cast<const __nv_bfloat16*>(X);
+  return pe::launch_gemm<pe::GEMM_RESIDUAL>(A, W, C, M, Nout, K, Nout, 0, args, status,
+                                            static_cast<cudaStream_t>(stream));
 }

@@ -51,7 +51,8 @@ int attn_run_tc(const void* qkv, const int4* tile_info, const int32_t* total_til
                 int64_t T, int nh, int half_window, void* out, int32_t* status, cudaStream_t st);
 
 // Process-wide switches (pe_set_option).
-enum Option : int { OPT_FUSED_GEGLU = 1, OPT_FUSED_ROPE = 2, OPT_LOCAL_ATTN_SINGLE_PASS = 3, OPT_COUNT };
+enum Option : int { OPT_FUSED_GEGLU = 1, OPT_FUSED_ROPE = 2, OPT_LOCAL_ATTN_SINGLE_PASS = 3,
+                    OPT_FUSED_RESIDUAL = 4, OPT_COUNT };
 int get_option(int key);
 
 }  // namespace pe

@@ -180,6 +180,23 @@ def linear_qkv_rope(x: Tensor, wqkv: Tensor, position_ids: Tensor, table: Tensor
     return out
 
 
+def linear_residual(x: Tensor, weight: Tensor, residual: Tensor, *, inplace: bool = False) -> Tensor:
+    """`residual + _linear(x, weight)` with the projection rounded to bf16 before the add, as one
+    kernel. `inplace=True` writes the sum over `residual`."""
+    x = _bf16_cuda(x, "x")
+    weight = _bf16_cuda(weight, "weight")
+    residual = _bf16_cuda(residual, "residual")
+    flat = x.reshape(-1, x.shape[-1])
+    res = residual.reshape(flat.shape[0], weight.shape[0])
+    out = res if inplace else torch.empty_like(res)
+    with _Call(x) as c:
+        _lib.check(c.lib.pe_gemm_residual_bf16(flat.data_ptr(), weight.data_ptr(), res.data_ptr(),
+                                               out.data_ptr(), flat.shape[0], weight.shape[0],
+                                               weight.shape[1], status_word(x.device).data_ptr(),
+                                               c.stream), "pe_gemm_residual_bf16")
+    return out.view(residual.shape)
+
+
 def attention_varlen_qkv(qkv: Tensor, cu_seqlens: Tensor, max_seqlen: int, n_heads: int,
                          half_window: int | None) -> Tensor:
     """Varlen attention on the fused, already-rotated `qkv [T, 3*n_heads*64]`;

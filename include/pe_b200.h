@@ -82,6 +82,10 @@ int pe_device_check(void);
 /* key 3 (PE_OPT_LOCAL_ATTN_SINGLE_PASS, default 1): sliding-window layers of long batches use the
  * one-pass tensor-memory kernel (1) or the generic online-softmax one (0). */
 #define PE_OPT_LOCAL_ATTN_SINGLE_PASS 3
+/* key 4 (PE_OPT_FUSED_RESIDUAL, default 1): Wo and the MLP's Wo add their result to the residual
+ * stream in the GEMM epilogue and the norms run as plain LayerNorms (1), or the projections are
+ * materialised and pe_add_ln adds them (0). */
+#define PE_OPT_FUSED_RESIDUAL 4
 int pe_set_option(int key, int value);
 
 /* ---- padding boundary ------------------------------------------------------ */
@@ -162,6 +166,13 @@ int pe_gemm_geglu_bf16(const void* A, const void* Wi, void* out, int64_t M, int 
 int pe_gemm_qkv_rope_bf16(const void* A, const void* Wqkv, void* qkv, int64_t M, int nh, int K,
                           const int64_t* position_ids, const void* table, int max_positions,
                           int32_t* status, void* stream);
+
+/* A projection and the residual add that follows it in one kernel:
+ * C = bf16(X + bf16(A W^T)), the value packed_encoders/ops.py:303-314 computes as x_new from the
+ * materialised projection (packed_encoders/forward.py:216-220 and the deferred MLP residual,
+ * 221-225).  X, C: bf16 [M, Nout]; C may be X (in place). */
+int pe_gemm_residual_bf16(const void* A, const void* W, const void* X, void* C, int64_t M, int Nout,
+                          int K, int32_t* status, void* stream);
 
 /* ---- attention -------------------------------------------------------------- */
 

@@ -69,10 +69,12 @@ def test_fused_and_unfused_epilogues_agree(pe, cuda_device, tiny_models):
         fused = pe.packed_forward(gpu, params, *args)
         _lib.check(lib.pe_set_option(_lib.OPT_FUSED_GEGLU, 0), "pe_set_option")
         _lib.check(lib.pe_set_option(_lib.OPT_FUSED_ROPE, 0), "pe_set_option")
+        _lib.check(lib.pe_set_option(_lib.OPT_FUSED_RESIDUAL, 0), "pe_set_option")
         unfused = pe.packed_forward(gpu, params, *args)
     finally:
         lib.pe_set_option(_lib.OPT_FUSED_GEGLU, 1)
         lib.pe_set_option(_lib.OPT_FUSED_ROPE, 1)
+        lib.pe_set_option(_lib.OPT_FUSED_RESIDUAL, 1)
     assert torch.equal(fused, unfused)
 
 

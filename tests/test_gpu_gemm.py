@@ -93,3 +93,18 @@ def test_fused_wqkv_rope_equals_two_kernels(pe, cuda_device, m, n_heads, k):
     assert torch.equal(fused, two)                 # same rounding points => same bits
     h = n_heads * 64
     assert torch.equal(fused[:, 2 * h:], ops._linear(a_d, w_d)[:, 2 * h:])   # v is not rotated
+
+
+@pytest.mark.parametrize("m,n,k", [(129, 768, 768), (1000, 768, 1152), (300, 1024, 2624), (200, 1792, 3840), (77, 72, 64)])
+def test_fused_residual_equals_two_steps(pe, cuda_device, m, n, k):
+    from flash_modernbert_b200 import ops
+
+    a, w, a_d, w_d = _inputs(m, n, k, cuda_device, seed=4)
+    res = torch.randn(m, n, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(cuda_device)
+    expected = res + ops._linear(a_d, w_d)          # bf16 + bf16 with one rounding, as add+LN forms x_new
+    fused = ops.linear_residual(a_d, w_d, res)
+    assert torch.equal(fused, expected)
+    inplace = res.clone()
+    assert ops.linear_residual(a_d, w_d, inplace, inplace=True).data_ptr() == inplace.data_ptr()
+    ops.check_status(cuda_device)
+    assert torch.equal(inplace, expected)
