@@ -329,6 +329,39 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
       // registers, O = P V is accumulated into the first 64 columns of the same region.
       int4 info = __ldg(tile_info + blockIdx.x / nh);
       uint32_t n = 0;
+      // The output row of item n - 1 is drained while item n is in flight: its P V runs during
+      // item n's S load and masking, so the wait below does not stall, and handing region
+      // (n - 1) & 1 back before item n's exp2 phase lets the MMA warp compute S of item n + 1
+      // under it.
+      bool prev_valid = false;
+      uint32_t prev_r = 0, prev_phase = 0;
+      float prev_inv = 0.f;
+      __nv_bfloat16* prev_orow = nullptr;  // nullptr: row past the end of its sequence
+      auto drain_prev = [&]() -> bool {
+        if (!mbar_wait(bar(TCB_O_FULL + prev_r), prev_phase, status, ST_ATTN_SOFTMAX_TIMEOUT)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t ov[32];
+          tmem_ld_32x32_nowait(lane_addr + prev_r * 256 + h * 32, ov);
+          tmem_ld_wait();
+          if (prev_orow != nullptr) {
+#pragma unroll
+            for (int d8 = 0; d8 < 4; ++d8) {
+              uint4 w4;
+              w4.x = pack_bf16(__uint_as_float(ov[d8 * 8 + 0]) * prev_inv, __uint_as_float(ov[d8 * 8 + 1]) * prev_inv);
+              w4.y = pack_bf16(__uint_as_float(ov[d8 * 8 + 2]) * prev_inv, __uint_as_float(ov[d8 * 8 + 3]) * prev_inv);
+              w4.z = pack_bf16(__uint_as_float(ov[d8 * 8 + 4]) * prev_inv, __uint_as_float(ov[d8 * 8 + 5]) * prev_inv);
+              w4.w = pack_bf16(__uint_as_float(ov[d8 * 8 + 6]) * prev_inv, __uint_as_float(ov[d8 * 8 + 7]) * prev_inv);
+              *reinterpret_cast<uint4*>(prev_orow + h * 32 + d8 * 8) = w4;
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(TCB_S_EMPTY + prev_r));  // the region may take the next S
+        return true;
+      };
       for (int item = blockIdx.x; item < total_items; item += stride_items, ++n) {
         const TcItem it = tc_make_item(info, item, nh, half_window);
         if (item + stride_items < total_items) info = __ldg(tile_info + (item + stride_items) / nh);
@@ -392,6 +425,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const float m_safe = (mx == -INFINITY) ? 0.f : mx * scale_log2;
+        if (prev_valid && !drain_prev()) break;  // also guarantees P V of item n - 1 is done with P
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         const uint32_t prow = sP + row * 128;
         const uint32_t sw = row & 7;
@@ -436,29 +470,13 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(TCB_P_FULL));
 
-        if (!mbar_wait(bar(TCB_O_FULL + r), (n >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) break;
-        tc_fence_after();
-        uint32_t ov[64];
-        tmem_ld_32x32_nowait(region, ov);
-        tmem_ld_32x32_nowait(region + 32, ov + 32);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(TCB_S_EMPTY + r));  // region r may take the next S
-        if (qi < it.len) {
-          const float inv = sum > 0.f ? 1.f / sum : 0.f;
-          __nv_bfloat16* orow = out + (int64_t(it.seq_begin) + qi) * H + it.head * 64;
-#pragma unroll
-          for (int d8 = 0; d8 < 8; ++d8) {
-            uint4 w4;
-            w4.x = pack_bf16(__uint_as_float(ov[d8 * 8 + 0]) * inv, __uint_as_float(ov[d8 * 8 + 1]) * inv);
-            w4.y = pack_bf16(__uint_as_float(ov[d8 * 8 + 2]) * inv, __uint_as_float(ov[d8 * 8 + 3]) * inv);
-            w4.z = pack_bf16(__uint_as_float(ov[d8 * 8 + 4]) * inv, __uint_as_float(ov[d8 * 8 + 5]) * inv);
-            w4.w = pack_bf16(__uint_as_float(ov[d8 * 8 + 6]) * inv, __uint_as_float(ov[d8 * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + d8 * 8) = w4;
-          }
-        }
+        prev_valid = true;
+        prev_r = r;
+        prev_phase = (n >> 1) & 1;
+        prev_inv = sum > 0.f ? 1.f / sum : 0.f;
+        prev_orow = qi < it.len ? out + (int64_t(it.seq_begin) + qi) * H + it.head * 64 : nullptr;
       }
+      if (prev_valid) drain_prev();
     } else {
     int4 info = __ldg(tile_info + blockIdx.x / nh);
     for (int item = blockIdx.x; ok && item < total_items; item += stride_items) {

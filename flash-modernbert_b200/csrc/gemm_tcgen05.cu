@@ -194,6 +194,22 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       ob ^= 1u;
     };
+    // GEMM_RESIDUAL: the warp's 32 x 64 block of X, fetched coalesced (instruction i covers rows
+    // 4i..4i+3) one block ahead of its use; with full 256-column tiles the chain runs across
+    // tiles, so no fetch latency is exposed after the first tile.
+    uint4 xr[2][8];
+    auto fetch_x = [&](uint4 (&dst)[8], int r0, int col) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = r0 + i * 4 + (lane >> 3);
+        const int cc = col + (lane & 7) * 8;
+        dst[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (r < M && cc + 8 <= n_out)
+          dst[i] = *reinterpret_cast<const uint4*>(rope.residual + size_t(r) * n_out + cc);
+      }
+    };
+    const bool res_chain = (MODE == GEMM_RESIDUAL) && (n_out % BN == 0);
+    bool res_ready = false;
     uint32_t acc = 0, acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int m0 = (tile / num_n) * BM;
@@ -245,23 +261,31 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // row-per-thread form through the staging buffer, adds, and stores the sum from the
         // same buffer.  X may be C: every block is read before the same warp overwrites it.
         const int col0 = nt * BN;
-        auto fetch = [&](uint4 (&xr)[8], int col) {
+        {  // warm L2 with this thread's row of the X tile this CTA handles next: by then the
+           // block fetches below find it on chip instead of paying a DRAM round trip per block
+          const int next = tile + gridDim.x;
+          if (next < num_tiles) {
+            const int nr = (next / num_n) * BM + q * 32 + lane;
+            const int nc = (next % num_n) * BN;
+            if (nr < M) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = row0 + i * 4 + (lane >> 3);
-            const int cc = col + (lane & 7) * 8;
-            xr[i] = make_uint4(0u, 0u, 0u, 0u);
-            if (r < M && cc + 8 <= n_out)
-              xr[i] = *reinterpret_cast<const uint4*>(rope.residual + size_t(r) * n_out + cc);
+              for (int c = 0; c < BN / 64; ++c)
+                if (nc + c * 64 < n_out)
+                  asm volatile("prefetch.global.L2 [%0];" ::"l"(rope.residual + size_t(nr) * n_out + nc + c * 64));
+            }
           }
-        };
-        uint4 xr[2][8];
-        fetch(xr[0], col0);
+        }
+        if (!res_ready) fetch_x(xr[0], row0, col0);  // first tile, or tiles with a ragged last chunk
 #pragma unroll
         for (int c = 0; c < BN / 64; ++c) {
           const int col = col0 + c * 64;
           if (col >= n_out) break;
-          if (c + 1 < BN / 64) fetch(xr[(c + 1) & 1], col + 64);
+          if (c + 1 < BN / 64) {
+            fetch_x(xr[(c + 1) & 1], row0, col + 64);
+          } else if (res_chain) {  // last chunk: start on the first block of this CTA's next tile
+            const int next = tile + gridDim.x;
+            if (next < num_tiles) fetch_x(xr[0], (next / num_n) * BM + q * 32, (next % num_n) * BN);
+          }
           uint32_t lo[32], hi[32];
           tmem_ld_32x32(t_addr + c * 64, lo);
           tmem_ld_32x32(t_addr + c * 64 + 32, hi);
@@ -308,6 +332,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           ob ^= 1u;
         }
+        res_ready = res_chain;
       } else if constexpr (!GEGLU) {
         const int col0 = nt * BN;
 #pragma unroll 1
