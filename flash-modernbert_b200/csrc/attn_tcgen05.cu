@@ -33,8 +33,10 @@ constexpr int TC_STAGES = 4;
 constexpr int TC_PREFETCH_ITEMS = 3;  // how many items ahead the producer warms L2
 constexpr int TC_TILE_BYTES = 128 * 64 * 2;          // one 128 x 64 bf16 tile (Q, K or V)
 constexpr int TC_P_BYTES = 128 * 128 * 2;            // one P buffer: two 128 x 64 halves
-constexpr int TC_THREADS = 192;  // 4 softmax warps + producer + MMA
-constexpr int TC_SMEM = TC_TILE_BYTES * (2 + 2 * TC_STAGES) + 2 * TC_P_BYTES + 1024 + 256;
+constexpr int TC_THREADS = 192;         // single-pass kernel: 4 softmax warps + producer + MMA
+constexpr int TC_THREADS_ONLINE = 320;  // online-softmax kernel: 8 softmax warps + producer + MMA
+constexpr int TC_SMEM = TC_TILE_BYTES * (2 + 2 * TC_STAGES) + 2 * TC_P_BYTES + 1024 /*align*/ +
+                        256 /*barriers*/ + 1024 /*row-sum mailbox*/;
 constexpr uint32_t TC_TMEM_COLS = 512;
 constexpr uint32_t TC_S_COL = 0;    // S[b] at columns b * 128
 constexpr uint32_t TC_O_COL = 256;  // O[b] at columns 256 + b * 64
@@ -101,7 +103,7 @@ __device__ __forceinline__ void tmem_ld_32x32_nowait(uint32_t taddr, uint32_t* v
 }
 
 template <bool LOCAL>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(LOCAL ? TC_THREADS : TC_THREADS_ONLINE, 1)
 attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __restrict__ tile_info,
                       const int32_t* __restrict__ total_tiles_ptr, int nh, int half_window,
                       __nv_bfloat16* __restrict__ out, int* status) {
@@ -117,7 +119,7 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
   auto bar = [&](int i) { return bar_base + 8u * i; };
   const uint32_t tmem_slot = bar_base + 8u * TCB_COUNT;
 
-  constexpr int NSW = 4;  // softmax warps; then one producer warp, one MMA warp
+  constexpr int NSW = LOCAL ? 4 : 8;  // softmax warps; then one producer warp, one MMA warp
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int H = nh * 64;
@@ -478,133 +480,150 @@ attn_varlen_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
       }
       if (prev_valid) drain_prev();
     } else {
-    int4 info = __ldg(tile_info + blockIdx.x / nh);
-    for (int item = blockIdx.x; ok && item < total_items; item += stride_items) {
-      const TcItem it = tc_make_item(info, item, nh, half_window);
-      if (item + stride_items < total_items)  // next item's descriptor, in flight during this one
-        info = __ldg(tile_info + (item + stride_items) / nh);
-      const int qi = it.q0 + row;  // position in the sequence
-      float acc[64];
+      // Full attention (and any band other than 64): online softmax over the key tiles.  Eight
+      // softmax warps: warps w and w + 4 own the same 32 query rows (same tensor-memory lanes) and
+      // split each row between them - warpgroup `hf` takes score columns [64 hf, 64 hf + 64) of
+      // every tile, writes that half of P, and keeps output dims [32 hf, 32 hf + 32).  Two warps
+      // per scheduler hide each other's exp2 / tensor-memory / dependency latencies and each
+      // thread's instruction stream is half as long.  The two halves of a row swap their tile
+      // maxima through shared memory (the tile's K buffer is dead once S is complete) and meet at
+      // a 64-thread named barrier; their partial row sums are combined once per item.
+      // After a bounded wait has given up, `ok` is false: waits are skipped but the loops and
+      // the named barriers still run to the end, so no warp is left alone at a barrier.
+      const uint32_t hf = warp >> 2;
+      const uint32_t pair_bar = 1 + wq;  // named barrier of warps wq and wq + 4
+      const uint32_t lbox = bar_base + 256;  // float[2][128]: per-item exchange of partial row sums
+      auto wait = [&](uint32_t barrier, uint32_t parity) {
+        if (ok && !mbar_wait(barrier, parity, status, ST_ATTN_SOFTMAX_TIMEOUT)) ok = false;
+      };
+      int4 info = __ldg(tile_info + blockIdx.x / nh);
+      uint32_t g = 0;  // key tiles consumed so far
+      for (int item = blockIdx.x; item < total_items; item += stride_items) {
+        const TcItem it = tc_make_item(info, item, nh, half_window);
+        if (item + stride_items < total_items)  // next item's descriptor, in flight during this one
+          info = __ldg(tile_info + (item + stride_items) / nh);
+        const int qi = it.q0 + row;  // position in the sequence
+        float acc[32];
 #pragma unroll
-      for (int d = 0; d < 64; ++d) acc[d] = 0.f;
-      float m_run = -INFINITY, l_run = 0.f;
-      // valid keys of this row, in sequence coordinates (empty for rows past the end)
-      int key_lo = 0, key_hi = it.len - 1;
-      if (half_window >= 0) {
-        key_lo = max(0, qi - half_window);
-        key_hi = min(it.len - 1, qi + half_window);
-      }
-      if (qi >= it.len) key_hi = -1;
-
-      for (int j = 0; j < it.n_kv; ++j, ++g) {
-        const uint32_t b = g & 1;
-        if (!mbar_wait(bar(TCB_S_FULL + b), (g >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) {
-          ok = false;
-          break;
+        for (int d = 0; d < 32; ++d) acc[d] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        int key_lo = 0, key_hi = it.len - 1;  // valid keys of this row (empty for rows past the end)
+        if (half_window >= 0) {
+          key_lo = max(0, qi - half_window);
+          key_hi = min(it.len - 1, qi + half_window);
         }
-        tc_fence_after();
-        uint32_t sv[128];
-        const uint32_t s_addr = lane_addr + TC_S_COL + b * 128;
-        tmem_ld_32x32_nowait(s_addr, sv);
-        tmem_ld_32x32_nowait(s_addr + 32, sv + 32);
-        tmem_ld_32x32_nowait(s_addr + 64, sv + 64);
-        tmem_ld_32x32_nowait(s_addr + 96, sv + 96);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(TCB_S_EMPTY + b));
+        if (qi >= it.len) key_hi = -1;
 
-        const int tile_key0 = it.kv_start + j * TC_BN;
-        const int c_lo = key_lo - tile_key0, c_hi = key_hi - tile_key0;  // valid columns [c_lo, c_hi]
-        const bool full = (c_lo <= 0) && (c_hi >= TC_BN - 1);
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
-        if (full) {
-#pragma unroll
-          for (int c = 0; c < 128; c += 2)
-            mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
-        } else {
-#pragma unroll
-          for (int c = 0; c < 128; ++c) {
-            const float v = (c >= c_lo && c <= c_hi) ? __uint_as_float(sv[c]) : -INFINITY;
-            sv[c] = __float_as_uint(v);
-            mx4[c & 3] = fmaxf(mx4[c & 3], v);
-          }
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        const float m_new = fmaxf(m_run, mx * scale_log2);
-        const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = ex2(m_run - m_safe);
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint32_t prow = sP + b * TC_P_BYTES + row * 128;
-#pragma unroll
-        for (int c8 = 0; c8 < 16; ++c8) {  // 16 chunks of 8 keys = 16 bytes of bf16
-          float p[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            p[e] = ex2(fmaf(__uint_as_float(sv[c8 * 8 + e]), scale_log2, -m_safe));
-            sum4[e & 3] += p[e];
-          }
-          const uint32_t addr = prow + (c8 >> 3) * TC_TILE_BYTES + (((c8 & 7) ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
-                       "r"(pack_bf16(p[0], p[1])), "r"(pack_bf16(p[2], p[3])),
-                       "r"(pack_bf16(p[4], p[5])), "r"(pack_bf16(p[6], p[7]))
-                       : "memory");
-        }
-        fence_proxy_async_smem();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(TCB_P_FULL + b));
-
-        if (j > 0) {  // fold in the previous tile's P V, then move to the new running maximum
-          const uint32_t pb = b ^ 1;
-          if (!mbar_wait(bar(TCB_O_FULL + pb), ((g - 1) >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) {
-            ok = false;
-            break;
-          }
+        for (int j = 0; j < it.n_kv; ++j, ++g) {
+          const uint32_t b = g & 1;
+          wait(bar(TCB_S_FULL + b), (g >> 1) & 1);
           tc_fence_after();
-          uint32_t ov[64];
-          tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64, ov);
-          tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64 + 32, ov + 32);
+          uint32_t sv[64];
+          const uint32_t s_addr = lane_addr + TC_S_COL + b * 128 + hf * 64;
+          tmem_ld_32x32_nowait(s_addr, sv);
+          tmem_ld_32x32_nowait(s_addr + 32, sv + 32);
           tmem_ld_wait();
-          if (__all_sync(0xffffffffu, alpha == 1.0f)) {  // common once the row maxima have settled
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(TCB_S_EMPTY + b));
+
+          const int col0 = it.kv_start + j * TC_BN + int(hf) * 64;       // key of this thread's column 0
+          const int c_lo = key_lo - col0, c_hi = key_hi - col0;          // valid columns [c_lo, c_hi]
+          const bool full = (c_lo <= 0) && (c_hi >= 63);
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
+          if (full) {
 #pragma unroll
-            for (int d = 0; d < 64; ++d) acc[d] += __uint_as_float(ov[d]);
+            for (int c = 0; c < 64; c += 2)
+              mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
           } else {
 #pragma unroll
-            for (int d = 0; d < 64; ++d) acc[d] = (acc[d] + __uint_as_float(ov[d])) * alpha;
+            for (int c = 0; c < 64; ++c) {
+              const float v = (c >= c_lo && c <= c_hi) ? __uint_as_float(sv[c]) : -INFINITY;
+              sv[c] = __float_as_uint(v);
+              mx4[c & 3] = fmaxf(mx4[c & 3], v);
+            }
+          }
+          float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          // swap the half-row maxima: mailbox = first KB of this tile's (dead) K buffer
+          const uint32_t mbox = sKV + (g % TC_STAGES) * 2 * TC_TILE_BYTES;
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(mbox + (hf * 128 + row) * 4), "f"(mx) : "memory");
+          asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+          float other;
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(mbox + ((hf ^ 1) * 128 + row) * 4) : "memory");
+          mx = fmaxf(mx, other);
+          const float m_new = fmaxf(m_run, mx * scale_log2);
+          const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+          const float alpha = ex2(m_run - m_safe);
+          float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+          const uint32_t prow = sP + b * TC_P_BYTES + hf * TC_TILE_BYTES + row * 128;
+#pragma unroll
+          for (int c8 = 0; c8 < 8; ++c8) {  // 8 chunks of 8 keys = 16 bytes of bf16
+            float p[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              p[e] = ex2(fmaf(__uint_as_float(sv[c8 * 8 + e]), scale_log2, -m_safe));
+              sum4[e & 3] += p[e];
+            }
+            const uint32_t addr = prow + ((c8 ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                         "r"(pack_bf16(p[0], p[1])), "r"(pack_bf16(p[2], p[3])),
+                         "r"(pack_bf16(p[4], p[5])), "r"(pack_bf16(p[6], p[7]))
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(TCB_P_FULL + b));
+
+          if (j > 0) {  // fold in the previous tile's P V, then move to the new running maximum
+            const uint32_t pb = b ^ 1;
+            wait(bar(TCB_O_FULL + pb), ((g - 1) >> 1) & 1);
+            tc_fence_after();
+            uint32_t ov[32];
+            tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64 + hf * 32, ov);
+            tmem_ld_wait();
+            if (__all_sync(0xffffffffu, alpha == 1.0f)) {  // common once the row maxima have settled
+#pragma unroll
+              for (int d = 0; d < 32; ++d) acc[d] += __uint_as_float(ov[d]);
+            } else {
+#pragma unroll
+              for (int d = 0; d < 32; ++d) acc[d] = (acc[d] + __uint_as_float(ov[d])) * alpha;
+            }
+          }
+          l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+          m_run = m_new;
+        }
+        {  // last tile's P V, the other half's row sum, normalise, store this half of the row
+          const uint32_t pb = (g - 1) & 1;
+          wait(bar(TCB_O_FULL + pb), ((g - 1) >> 1) & 1);
+          tc_fence_after();
+          uint32_t ov[32];
+          tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64 + hf * 32, ov);
+          tmem_ld_wait();
+          tc_fence_before();
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(lbox + (hf * 128 + row) * 4), "f"(l_run) : "memory");
+          asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+          float l_other;
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(l_other) : "r"(lbox + ((hf ^ 1) * 128 + row) * 4) : "memory");
+          const float l_all = l_run + l_other;  // both halves use the same running maximum
+          if (ok && qi < it.len) {
+            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+            __nv_bfloat16* orow = out + (int64_t(it.seq_begin) + qi) * H + it.head * 64 + hf * 32;
+#pragma unroll
+            for (int d8 = 0; d8 < 4; ++d8) {
+              float o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[e] = (acc[d8 * 8 + e] + __uint_as_float(ov[d8 * 8 + e])) * inv;
+              uint4 w;
+              w.x = pack_bf16(o[0], o[1]);
+              w.y = pack_bf16(o[2], o[3]);
+              w.z = pack_bf16(o[4], o[5]);
+              w.w = pack_bf16(o[6], o[7]);
+              *reinterpret_cast<uint4*>(orow + d8 * 8) = w;
+            }
           }
         }
-        l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-        m_run = m_new;
       }
-      if (!ok) break;
-      {  // last tile's P V, normalise, store the row
-        const uint32_t pb = (g - 1) & 1;
-        if (!mbar_wait(bar(TCB_O_FULL + pb), ((g - 1) >> 1) & 1, status, ST_ATTN_SOFTMAX_TIMEOUT)) break;
-        tc_fence_after();
-        uint32_t ov[64];
-        tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64, ov);
-        tmem_ld_32x32_nowait(lane_addr + TC_O_COL + pb * 64 + 32, ov + 32);
-        tmem_ld_wait();
-        tc_fence_before();
-        if (qi < it.len) {
-          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-          __nv_bfloat16* orow = out + (int64_t(it.seq_begin) + qi) * H + it.head * 64;
-#pragma unroll
-          for (int d8 = 0; d8 < 8; ++d8) {
-            float o[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = (acc[d8 * 8 + e] + __uint_as_float(ov[d8 * 8 + e])) * inv;
-            uint4 w;
-            w.x = pack_bf16(o[0], o[1]);
-            w.y = pack_bf16(o[2], o[3]);
-            w.z = pack_bf16(o[4], o[5]);
-            w.w = pack_bf16(o[6], o[7]);
-            *reinterpret_cast<uint4*>(orow + d8 * 8) = w;
-          }
-        }
-      }
-    }
     }
   }
 
@@ -637,7 +656,7 @@ int attn_run_tc(const void* qkv, const int4* tile_info, const int32_t* total_til
     attn_varlen_tc_kernel<true><<<grid, TC_THREADS, TC_SMEM, st>>>(
         tm, tile_info, total_tiles, nh, half_window, static_cast<__nv_bfloat16*>(out), status);
   else
-    attn_varlen_tc_kernel<false><<<grid, TC_THREADS, TC_SMEM, st>>>(
+    attn_varlen_tc_kernel<false><<<grid, TC_THREADS_ONLINE, TC_SMEM, st>>>(
         tm, tile_info, total_tiles, nh, half_window, static_cast<__nv_bfloat16*>(out), status);
   PE_LAUNCH_CHECK("attn_varlen_tc_kernel");
   return PE_OK;
