@@ -33,7 +33,7 @@ METRIC = "packed tokens/sec, ModernBERT-base doc encode bf16"
 # DRAM bytes (read + write) of the four GEMM launches of one ModernBERT-base layer per token,
 # from one ncu capture on a 71,567-token slice of the workload (profiles/gemm_tcgen05_cfg3q.md);
 # GEMM traffic grows in proportion to the rows, so a full launch is this times its tokens.
-NCU_GEMM_DRAM_BYTES_PER_TOKEN = 1041.1e6 / 71567
+NCU_GEMM_DRAM_BYTES_PER_TOKEN = 1256.2e6 / 71567
 UNIT = "tokens/s"
 
 
@@ -380,7 +380,7 @@ def run_ours(args) -> None:
             "traffic": (round(NCU_GEMM_DRAM_BYTES_PER_TOKEN * batch.total_tokens / 1e9, 3)
                         if arch == "base" else None),
             "traffic_unit": "GB per layer (four launches), ncu on a 71,567-token slice scaled by tokens",
-            "algorithmic_gb": round(16896 * batch.total_tokens / 1e9, 3), "per_shape": {k: {"ms": v["ms"], "tflops": v["tflops"]} for k, v in gemm.items()},
+            "algorithmic_gb": round(19968 * batch.total_tokens / 1e9, 3), "per_shape": {k: {"ms": v["ms"], "tflops": v["tflops"]} for k, v in gemm.items()},
         },
         "step_model": {
             "gemm_tflop": round(work["gemm_flops"] / 1e12, 2), "attn_tflop": round(work["attn_flops"] / 1e12, 2),
