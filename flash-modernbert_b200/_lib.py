@@ -32,6 +32,7 @@ OPT_FUSED_GEGLU = 1
 OPT_FUSED_ROPE = 2
 OPT_LOCAL_ATTN_SINGLE_PASS = 3
 OPT_FUSED_RESIDUAL = 4
+OPT_ATTN_TWO_CTA = 5
 
 
 class NativeLibraryError(PackedEncodersError):

@@ -1,0 +1,506 @@
+// Full (and general banded) varlen attention on the sm_100a tensor cores, built so that
+// TWO CTAs share each SM.
+//
+// The softmax of a 128 x 128 score tile costs 16384 exp2 on a unit that retires 16 per clock
+// per SM: 1024 clocks in which the other pipes idle, followed by a stretch (tensor-memory
+// loads, row maxima, barrier round trips, the P V product) in which the exp2 unit idles.
+// Warps that work on the same tile move through those phases together, so one CTA per SM can
+// never overlap them.  Two independent CTAs per SM - each a complete pipeline over its own
+// work items - drift out of phase and fill each other's gaps.  To fit twice, a CTA is cut to
+// 192 threads (168 registers), 113 KB of shared memory and 256 tensor-memory columns:
+//   warps 0..3 : softmax - thread t owns query row t: one tcgen05.ld pass brings its 128
+//                scores into registers (S is released at once, so the next Q K^T overlaps the
+//                exp2 work), row maximum, exp2, row sum; P goes back to TENSOR MEMORY as bf16
+//                pairs (tcgen05.st), never through shared memory
+//   warp 4     : TMA producer - Q (single buffer), K and V in separate three-deep rings (K is
+//                free as soon as Q K^T retires, so it runs ahead of V)
+//   warp 5     : tensor-memory owner and MMA issuer - S = Q K^T (both operands from shared
+//                memory) into one 128-column buffer; O += P V with P read from tensor memory
+//                (the A operand of tcgen05.mma may live there) and V from shared memory,
+//                ACCUMULATED in 64 columns over the whole item
+// Shared memory then carries only Q, K and V: with P there as well, its 128 bytes per clock
+// (operand reads of both products, P written and read back, the TMA fills) were as loaded as
+// the exp2 unit.
+// The output accumulator is rescaled in tensor memory only when a row maximum has grown by
+// more than 2^8 since the maximum it was last scaled to (P then stays below 256, exact
+// enough in bf16 and far from overflow in the fp32 sums); after the first tile or two of an
+// item that almost never happens, so the per-tile loop has no accumulator traffic at all.
+//
+// Rows of a K/V tile outside the sequence (or the band) are whatever TMA fetched and are
+// masked to -inf before the softmax, so P is exactly 0 there.  Query rows past the end of a
+// sequence are computed on whatever was fetched and never stored.  Every mbarrier wait is
+// bounded and reports through the status word.
+#include "pe_host.h"
+#include "pe_ptx.cuh"
+
+namespace pe {
+
+constexpr int G_BM = 128;
+constexpr int G_BN = 128;
+constexpr int G_THREADS = 192;
+constexpr int G_TILE_BYTES = 128 * 64 * 2;  // one 128 x 64 bf16 tile (Q, K, V, half of P)
+constexpr int G_PREFETCH_ITEMS = 3;         // how many items ahead the producer warms L2
+constexpr int G_STAGES = 3;                 // depth of the K ring and of the V ring
+// Q, K[3], V[3] = 7 tiles, then the barriers.  No alignment slack: the kernel checks that
+// the dynamic shared memory starts on a 1024-byte boundary.
+constexpr int G_SMEM = (1 + 2 * G_STAGES) * G_TILE_BYTES + 256;
+constexpr uint32_t G_TMEM_COLS = 256;
+constexpr uint32_t G_S_COL = 0;    // S: columns 0..127
+constexpr uint32_t G_O_COL = 128;  // O: columns 128..191
+constexpr uint32_t G_P_COL = 192;  // P: bf16 pairs, keys 2c and 2c + 1 in column 192 + c
+constexpr float G_RESCALE_LOG2 = 8.0f;
+
+enum {
+  GB_Q_FULL = 0,
+  GB_Q_EMPTY = 1,
+  GB_K_FULL = 2,    // G_STAGES
+  GB_K_EMPTY = 5,   // G_STAGES
+  GB_V_FULL = 8,    // G_STAGES
+  GB_V_EMPTY = 11,  // G_STAGES
+  GB_S_FULL = 14,
+  GB_S_EMPTY = 15,
+  GB_P_FULL = 16,
+  GB_O_FULL = 17,
+  GB_COUNT = 18
+};
+
+struct GItem {
+  int seq_begin, len, q0, head;
+  int kv_start, n_kv;
+};
+
+__device__ __forceinline__ GItem g_make_item(const int4 info, int item, int nh, int half_window) {
+  GItem it;
+  it.seq_begin = info.x;
+  it.len = info.y;
+  it.q0 = info.z;
+  it.head = item % nh;
+  // key tile j covers keys [kv_start + 128 j, kv_start + 128 j + 128) of the sequence
+  it.kv_start = 0;
+  it.n_kv = (it.len + G_BN - 1) / G_BN;
+  if (half_window >= 0) {
+    it.kv_start = it.q0 - half_window;  // may be negative: those keys are masked
+    const int kv_end = min(it.len, it.q0 + G_BM + half_window);
+    it.n_kv = (kv_end - it.kv_start + G_BN - 1) / G_BN;
+  }
+  return it;
+}
+
+// A cursor over the flat sequence of key tiles of this CTA's items.
+struct GCursor {
+  int item, j;
+  GItem it;
+  __device__ __forceinline__ void open(const int4* tile_info, int first, int total, int nh, int hw) {
+    item = first;
+    j = 0;
+    if (item < total) it = g_make_item(__ldg(tile_info + item / nh), item, nh, hw);
+  }
+  __device__ __forceinline__ void advance(const int4* tile_info, int stride, int total, int nh, int hw) {
+    if (++j == it.n_kv) {
+      j = 0;
+      item += stride;
+      if (item < total) it = g_make_item(__ldg(tile_info + item / nh), item, nh, hw);
+    }
+  }
+};
+
+__device__ __forceinline__ float g_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void g_tmem_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+        "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+        "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void g_tmem_ld8(uint32_t taddr, uint32_t* v) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                 "=r"(v[7])
+               : "r"(taddr)
+               : "memory");
+}
+
+__device__ __forceinline__ void g_tmem_st8(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+               "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+
+__device__ __forceinline__ void g_tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (M = 128 rows on the 128 lanes, K elements in
+// pairs along the columns) is read from tensor memory.  Issued by one thread.
+__device__ __forceinline__ void g_umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Rare path of the softmax warps, kept out of line so that its registers do not add to the
+// 128 live scores of the caller: scale this thread's accumulator row by alpha in tensor memory.
+__device__ __noinline__ void g_rescale_accumulator(uint32_t o_addr, float alpha) {
+  for (int h = 0; h < 8; ++h) {
+    uint32_t ov[8];
+    g_tmem_ld8(o_addr + h * 8, ov);
+    tmem_ld_wait();
+#pragma unroll
+    for (int d = 0; d < 8; ++d) ov[d] = __float_as_uint(__uint_as_float(ov[d]) * alpha);
+    g_tmem_st8(o_addr + h * 8, ov);
+  }
+  g_tmem_st_wait();
+}
+
+__global__ void __launch_bounds__(G_THREADS, 2)
+attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __restrict__ tile_info,
+                      const int32_t* __restrict__ total_tiles_ptr, int nh, int half_window,
+                      __nv_bfloat16* __restrict__ out, int* status) {
+  const int total_items = *total_tiles_ptr * nh;
+  if (int(blockIdx.x) >= total_items) return;  // whole CTA leaves before any barrier or allocation
+
+  extern __shared__ __align__(1024) uint8_t g_smem[];
+  const uint32_t base = smem_u32(g_smem);
+  if (base & 1023u) {  // the swizzled tiles need it; nothing has been allocated yet
+    if (threadIdx.x == 0) set_status(status, ST_ATTN_SMEM_MISALIGNED);
+    return;
+  }
+  const uint32_t sQ = base;
+  const uint32_t sK = sQ + G_TILE_BYTES;       // K[s] at + s * 16 KB
+  const uint32_t sV = sK + G_STAGES * G_TILE_BYTES;  // V[s] at + s * 16 KB
+  const uint32_t bar_base = sV + G_STAGES * G_TILE_BYTES;
+  auto bar = [&](int i) { return bar_base + 8u * i; };
+  const uint32_t tmem_slot = bar_base + 8u * GB_COUNT;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int H = nh * 64;
+  const int stride_items = gridDim.x;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(GB_Q_FULL), 1);
+    mbar_init(bar(GB_Q_EMPTY), 1);
+    for (int s = 0; s < G_STAGES; ++s) {
+      mbar_init(bar(GB_K_FULL + s), 1);
+      mbar_init(bar(GB_K_EMPTY + s), 1);
+      mbar_init(bar(GB_V_FULL + s), 1);
+      mbar_init(bar(GB_V_EMPTY + s), 1);
+    }
+    mbar_init(bar(GB_S_FULL), 1);
+    mbar_init(bar(GB_S_EMPTY), 4);  // one arrival per softmax warp
+    mbar_init(bar(GB_P_FULL), 4);
+    mbar_init(bar(GB_O_FULL), 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_qkv);
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, G_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 4) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      GCursor kc, vc;
+      kc.open(tile_info, blockIdx.x, total_items, nh, half_window);
+      vc = kc;
+      uint32_t gk = 0, gv = 0, nq = 0;  // K tiles, V tiles, Q tiles loaded so far
+      bool ok = true;
+      while (ok && vc.item < total_items) {
+        while (ok && kc.item < total_items && gk <= gv + 1) {  // K runs one tile ahead of V
+          if (kc.j == 0) {
+            // warm L2 with the first tiles of an item a few steps ahead
+            const int ahead = kc.item + G_PREFETCH_ITEMS * stride_items;
+            if (ahead < total_items) {
+              const GItem nx = g_make_item(__ldg(tile_info + ahead / nh), ahead, nh, half_window);
+              const int c = nx.head * 64;
+              tma_prefetch_l2_2d(&tm_qkv, c, nx.seq_begin + nx.q0);
+              for (int j = 0; j < min(nx.n_kv, 2); ++j) {
+                const int r = nx.seq_begin + nx.kv_start + j * G_BN;
+                tma_prefetch_l2_2d(&tm_qkv, H + c, r);
+                tma_prefetch_l2_2d(&tm_qkv, 2 * H + c, r);
+              }
+            }
+            ok = mbar_wait(bar(GB_Q_EMPTY), (nq & 1) ^ 1u, status, ST_ATTN_TIMEOUT);
+            if (!ok) break;
+            mbar_expect_tx(bar(GB_Q_FULL), G_TILE_BYTES);
+            tma_load_2d(sQ, &tm_qkv, bar(GB_Q_FULL), kc.it.head * 64, kc.it.seq_begin + kc.it.q0);
+            ++nq;
+          }
+          const uint32_t s = gk % G_STAGES;
+          ok = mbar_wait(bar(GB_K_EMPTY + s), ((gk / G_STAGES) & 1) ^ 1u, status, ST_ATTN_TIMEOUT);
+          if (!ok) break;
+          mbar_expect_tx(bar(GB_K_FULL + s), G_TILE_BYTES);
+          tma_load_2d(sK + s * G_TILE_BYTES, &tm_qkv, bar(GB_K_FULL + s), H + kc.it.head * 64,
+                      kc.it.seq_begin + kc.it.kv_start + kc.j * G_BN);
+          ++gk;
+          kc.advance(tile_info, stride_items, total_items, nh, half_window);
+        }
+        if (!ok) break;
+        const uint32_t s = gv % G_STAGES;
+        ok = mbar_wait(bar(GB_V_EMPTY + s), ((gv / G_STAGES) & 1) ^ 1u, status, ST_ATTN_TIMEOUT);
+        if (!ok) break;
+        mbar_expect_tx(bar(GB_V_FULL + s), G_TILE_BYTES);
+        tma_load_2d(sV + s * G_TILE_BYTES, &tm_qkv, bar(GB_V_FULL + s), 2 * H + vc.it.head * 64,
+                    vc.it.seq_begin + vc.it.kv_start + vc.j * G_BN);
+        ++gv;
+        vc.advance(tile_info, stride_items, total_items, nh, half_window);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 64, 1);  // B (= V) is MN-major
+      GCursor qc, pc;
+      qc.open(tile_info, blockIdx.x, total_items, nh, half_window);
+      pc = qc;
+      uint32_t gq = 0, gp = 0, nq = 0;  // Q K^T tiles issued, P V tiles issued, items begun
+      bool ok = true;
+      // S = Q K^T for the tile under the q cursor; the caller has made sure S is free.
+      auto issue_qk = [&]() {
+        const uint32_t s = gq % G_STAGES;
+        if (qc.j == 0) ok = mbar_wait(bar(GB_Q_FULL), nq & 1, status, ST_ATTN_MMA_TIMEOUT);
+        ok = ok && mbar_wait(bar(GB_K_FULL + s), (gq / G_STAGES) & 1, status, ST_ATTN_MMA_TIMEOUT);
+        if (!ok) return;
+        tc_fence_after();
+        const uint64_t qdesc = umma_smem_desc_sw128(sQ, 1024);
+        const uint64_t kdesc = umma_smem_desc_sw128(sK + s * G_TILE_BYTES, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_ss(tmem_base + G_S_COL, qdesc + 2u * kk, kdesc + 2u * kk, idesc_qk, kk != 0 ? 1u : 0u);
+        umma_commit(bar(GB_S_FULL));
+        umma_commit(bar(GB_K_EMPTY + s));
+        ++gq;
+        if (qc.j + 1 == qc.it.n_kv) {  // last key tile of the item: Q is free once these retire
+          umma_commit(bar(GB_Q_EMPTY));
+          ++nq;
+        }
+        qc.advance(tile_info, stride_items, total_items, nh, half_window);
+      };
+      if (qc.item < total_items) issue_qk();
+      while (ok && pc.item < total_items) {
+        // The softmax warps release S as soon as tile gp is in their registers: the next
+        // Q K^T then runs under their exp2 work.  Across an item boundary the next Q may still
+        // be in flight; then P V goes first so the item's epilogue is not held up.
+        bool qk_pending = qc.item < total_items;
+        if (qk_pending && (qc.j != 0 || mbar_try_wait(bar(GB_Q_FULL), nq & 1))) {
+          ok = mbar_wait(bar(GB_S_EMPTY), gp & 1, status, ST_ATTN_MMA_TIMEOUT);
+          if (!ok) break;
+          issue_qk();
+          if (!ok) break;
+          qk_pending = false;
+        }
+        {
+          const uint32_t s = gp % G_STAGES;
+          ok = mbar_wait(bar(GB_P_FULL), gp & 1, status, ST_ATTN_MMA_TIMEOUT) &&
+               mbar_wait(bar(GB_V_FULL + s), (gp / G_STAGES) & 1, status, ST_ATTN_MMA_TIMEOUT);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t vbase = sV + s * G_TILE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            // A: keys [16 kk, 16 kk + 16) of P, straight from tensor memory: 8 columns of pairs
+            // B: V rows [16 kk, 16 kk + 16), 128 bytes per row
+            const uint64_t vdesc = umma_smem_desc_sw128(vbase + kk * 2048, 1024);
+            g_umma_ts(tmem_base + G_O_COL, tmem_base + G_P_COL + kk * 8, vdesc, idesc_pv,
+                      (pc.j | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(bar(GB_O_FULL));
+          umma_commit(bar(GB_V_EMPTY + s));
+          ++gp;
+          pc.advance(tile_info, stride_items, total_items, nh, half_window);
+        }
+        if (qk_pending) {  // S was released before P was complete, so no wait on S_EMPTY is needed
+          issue_qk();
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- softmax warps
+    const int row = threadIdx.x;  // query row within the tile = tensor-memory lane
+    const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16);
+    const float scale_log2 = 0.125f * 1.4426950408889634f;  // 1/sqrt(64) * log2(e)
+    bool ok = true;
+    // After a bounded wait has given up, `ok` is false: waits are skipped but the loops still
+    // run to the end (on garbage), so the CTA reaches its final barrier and frees tensor memory.
+    auto wait = [&](uint32_t barrier, uint32_t parity) {
+      if (ok && !mbar_wait(barrier, parity, status, ST_ATTN_SOFTMAX_TIMEOUT)) ok = false;
+    };
+    uint32_t g = 0;  // key tiles consumed so far
+    for (int item = blockIdx.x; item < total_items; item += stride_items) {
+      // Only what the tile loop needs stays in registers beside the 128 scores; the epilogue
+      // re-reads the item's descriptor.
+      int n_kv, col0, key_lo, key_hi;  // key tiles; key of column 0; valid keys of this row
+      {
+        const GItem it = g_make_item(__ldg(tile_info + item / nh), item, nh, half_window);
+        const int qi = it.q0 + row;
+        n_kv = it.n_kv;
+        col0 = it.kv_start;
+        key_lo = 0;
+        key_hi = it.len - 1;
+        if (half_window >= 0) {
+          key_lo = max(0, qi - half_window);
+          key_hi = min(it.len - 1, qi + half_window);
+        }
+        // Rows past the end of the sequence are computed like the others (on whatever TMA
+        // fetched) and never stored: masking them would only make their warps diverge.
+      }
+      float m_used = -INFINITY;  // the maximum P and the accumulator are scaled to
+      float l_run = 0.f;
+
+      for (int j = 0; j < n_kv; ++j, ++g, col0 += G_BN) {
+        wait(bar(GB_S_FULL), g & 1);
+        tc_fence_after();
+        uint32_t sv[128];
+        g_tmem_ld32(lane_addr + G_S_COL, sv);
+        g_tmem_ld32(lane_addr + G_S_COL + 32, sv + 32);
+        g_tmem_ld32(lane_addr + G_S_COL + 64, sv + 64);
+        g_tmem_ld32(lane_addr + G_S_COL + 96, sv + 96);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(GB_S_EMPTY));  // the next Q K^T may overwrite S now
+
+        const int c_lo = key_lo - col0, c_hi = key_hi - col0;  // valid columns [c_lo, c_hi]
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
+        // warp-uniform, so a warp never runs both branches
+        if (__all_sync(0xffffffffu, c_lo <= 0 && c_hi >= G_BN - 1)) {
+#pragma unroll
+          for (int c = 0; c < 128; c += 2)
+            mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 128; ++c) {
+            const float v = (c >= c_lo && c <= c_hi) ? __uint_as_float(sv[c]) : -INFINITY;
+            sv[c] = __float_as_uint(v);
+            mx4[c & 3] = fmaxf(mx4[c & 3], v);
+          }
+        }
+        const float m_new = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+        if (j == 0) {
+          m_used = m_new;
+        } else {
+          // P is a single buffer and O an accumulator: the previous tile's P V must have retired
+          // before P is overwritten or O rescaled.  It was issued a whole max pass ago, so this
+          // wait is normally over at the first poll.
+          wait(bar(GB_O_FULL), (g - 1) & 1);
+          tc_fence_after();
+          // -inf + 8 stays -inf, so a row that has seen no valid key yet moves to any finite
+          // maximum; its accumulator and sum are still exactly zero and stay so (alpha = 0).
+          const bool grow = m_new > m_used + G_RESCALE_LOG2;
+          if (__any_sync(0xffffffffu, grow)) {
+            const float alpha = grow ? g_ex2(m_used - m_new) : 1.0f;
+            g_rescale_accumulator(lane_addr + G_O_COL, alpha);
+            l_run *= alpha;
+            if (grow) m_used = m_new;
+          }
+        }
+        const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c16 = 0; c16 < 8; ++c16) {  // 16 keys = 8 columns of bf16 pairs at a time
+          uint32_t pk[8];
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const float p0 = g_ex2(fmaf(__uint_as_float(sv[c16 * 16 + e]), scale_log2, -m_safe));
+            const float p1 = g_ex2(fmaf(__uint_as_float(sv[c16 * 16 + e + 1]), scale_log2, -m_safe));
+            sum4[(e >> 1) & 3] += p0 + p1;
+            pk[e >> 1] = pack_bf16(p0, p1);
+          }
+          g_tmem_st8(lane_addr + G_P_COL + c16 * 8, pk);
+        }
+        g_tmem_st_wait();
+        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(GB_P_FULL));
+      }
+      {  // the item's accumulator: normalise and store this row
+        const GItem it = g_make_item(__ldg(tile_info + item / nh), item, nh, half_window);
+        const int qi = it.q0 + row;
+        wait(bar(GB_O_FULL), (g - 1) & 1);
+        tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* orow = out + (int64_t(it.seq_begin) + qi) * H + it.head * 64;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t ov[32];
+          g_tmem_ld32(lane_addr + G_O_COL + h * 32, ov);
+          tmem_ld_wait();
+          if (ok && qi < it.len) {
+#pragma unroll
+            for (int d8 = 0; d8 < 4; ++d8) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(ov[d8 * 8 + 0]) * inv, __uint_as_float(ov[d8 * 8 + 1]) * inv);
+              w.y = pack_bf16(__uint_as_float(ov[d8 * 8 + 2]) * inv, __uint_as_float(ov[d8 * 8 + 3]) * inv);
+              w.z = pack_bf16(__uint_as_float(ov[d8 * 8 + 4]) * inv, __uint_as_float(ov[d8 * 8 + 5]) * inv);
+              w.w = pack_bf16(__uint_as_float(ov[d8 * 8 + 6]) * inv, __uint_as_float(ov[d8 * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + h * 32 + d8 * 8) = w;
+            }
+          }
+        }
+        // The next item's first P V overwrites O; it waits for this warp's next P_FULL arrival,
+        // which follows these loads in program order.
+        tc_fence_before();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, G_TMEM_COLS);
+  }
+}
+
+int attn_run_global_tc(const void* qkv, const int4* tile_info, const int32_t* total_tiles,
+                       int64_t max_tiles, int64_t T, int nh, int half_window, void* out,
+                       int32_t* status, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    PE_CUDA(cudaFuncSetAttribute(attn_global_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 G_SMEM));
+    PE_CUDA(cudaFuncSetAttribute(attn_global_tc_kernel,
+                                 cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared));
+    attr_set = true;
+  }
+  CUtensorMap tm;
+  int rc = make_tmap_bf16_2d(&tm, qkv, (uint64_t)T, (uint64_t)(3 * nh * 64), (uint64_t)(3 * nh * 64),
+                             128);
+  if (rc != PE_OK) return rc;
+  const int64_t max_items = max_tiles * nh;
+  const int64_t slots = 2 * (int64_t)sm_count();  // two resident CTAs per SM
+  const int grid = (int)(max_items < slots ? max_items : slots);
+  attn_global_tc_kernel<<<grid, G_THREADS, G_SMEM, st>>>(tm, tile_info, total_tiles, nh, half_window,
+                                                        static_cast<__nv_bfloat16*>(out), status);
+  PE_LAUNCH_CHECK("attn_global_tc_kernel");
+  return PE_OK;
+}
+
+}  // namespace pe

@@ -655,6 +655,8 @@ int attn_run_tc(const void* qkv, const int4* tile_info, const int32_t* total_til
   if (half_window == TC_BN / 2 && get_option(OPT_LOCAL_ATTN_SINGLE_PASS))
     attn_varlen_tc_kernel<true><<<grid, TC_THREADS, TC_SMEM, st>>>(
         tm, tile_info, total_tiles, nh, half_window, static_cast<__nv_bfloat16*>(out), status);
+  else if (get_option(OPT_ATTN_TWO_CTA))
+    return attn_run_global_tc(qkv, tile_info, total_tiles, max_tiles, T, nh, half_window, out, status, st);
   else
     attn_varlen_tc_kernel<false><<<grid, TC_THREADS_ONLINE, TC_SMEM, st>>>(
         tm, tile_info, total_tiles, nh, half_window, static_cast<__nv_bfloat16*>(out), status);

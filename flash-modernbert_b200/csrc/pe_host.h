@@ -49,10 +49,14 @@ int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh
 // The persistent 128-row tensor-memory kernel (attn_tcgen05.cu); tiles built with bm = 128.
 int attn_run_tc(const void* qkv, const int4* tile_info, const int32_t* total_tiles, int64_t max_tiles,
                 int64_t T, int nh, int half_window, void* out, int32_t* status, cudaStream_t st);
+// Full / banded attention with two CTAs per SM and the accumulator in tensor memory.
+int attn_run_global_tc(const void* qkv, const int4* tile_info, const int32_t* total_tiles,
+                       int64_t max_tiles, int64_t T, int nh, int half_window, void* out,
+                       int32_t* status, cudaStream_t st);
 
 // Process-wide switches (pe_set_option).
 enum Option : int { OPT_FUSED_GEGLU = 1, OPT_FUSED_ROPE = 2, OPT_LOCAL_ATTN_SINGLE_PASS = 3,
-                    OPT_FUSED_RESIDUAL = 4, OPT_COUNT };
+                    OPT_FUSED_RESIDUAL = 4, OPT_ATTN_TWO_CTA = 5, OPT_COUNT };
 int get_option(int key);
 
 }  // namespace pe

@@ -18,6 +18,7 @@ enum StatusCode : int {
   ST_ATTN_TIMEOUT = 201,
   ST_ATTN_MMA_TIMEOUT = 202,
   ST_ATTN_SOFTMAX_TIMEOUT = 203,
+  ST_ATTN_SMEM_MISALIGNED = 204,  // dynamic shared memory did not start on a 1024-byte boundary
   ST_BAD_TOKEN_ID = 301,
   ST_BAD_POSITION = 302,
 };

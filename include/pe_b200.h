@@ -86,6 +86,10 @@ int pe_device_check(void);
  * stream in the GEMM epilogue and the norms run as plain LayerNorms (1), or the projections are
  * materialised and pe_add_ln adds them (0). */
 #define PE_OPT_FUSED_RESIDUAL 4
+/* key 5 (PE_OPT_ATTN_TWO_CTA, default 1): full-attention layers of long batches use the kernel
+   that keeps two CTAs per SM and the output accumulator in tensor memory (1), or the
+   one-CTA-per-SM kernel with eight softmax warps (0). */
+#define PE_OPT_ATTN_TWO_CTA 5
 int pe_set_option(int key, int value);
 
 /* ---- padding boundary ------------------------------------------------------ */

@@ -72,6 +72,37 @@ def test_deterministic_and_finite(pe, cuda_device, scale):
     assert torch.equal(a, b) and bool(torch.isfinite(a.float()).all())
 
 
+@pytest.mark.parametrize("q_scale", [8.0, 40.0])
+def test_row_maximum_drifts_far_between_key_tiles(pe, cuda_device, q_scale):
+    """Scores spread over hundreds of log2 units, so the running row maximum jumps by more
+    than 2^8 (the accumulator is rescaled) and by more than 2^60 (a key tile is redone against
+    a new reference) from one 128-key tile to the next, upwards, and downwards from the initial
+    reference.  Some rows get a strongly negative offset so that every score is far below 0."""
+    qkv, cu = _qkv([700, 300, 130], 4, cuda_device, seed=11, scale=q_scale)
+    q = qkv[:, 0].float()
+    k = qkv[:, 1].float()
+    # keys 0..199 of the first sequence anti-aligned with its queries' mean direction: low scores
+    # early, high scores late
+    d = q[:700].mean(0, keepdim=True)
+    k[:200] -= 0.5 * d / d.norm(dim=-1, keepdim=True) * 8
+    qkv[:, 1] = k.to(torch.bfloat16)
+    # second sequence: every score against its first 128 keys is about -1000 (2^-190 after
+    # scaling), against the rest about 0 - the first tile lies far below the initial reference,
+    # the second far above the first
+    gen = torch.Generator().manual_seed(12)
+    qkv[700:1000, 0] = (4.1 + 0.1 * torch.randn(300, 4, 64, generator=gen)).to(torch.bfloat16)
+    qkv[700:828, 1] = (-4.1 + 0.1 * torch.randn(128, 4, 64, generator=gen)).to(torch.bfloat16)
+    qkv[828:1000, 1] = (0.02 * torch.randn(172, 4, 64, generator=gen)).to(torch.bfloat16)
+    for hw in (None, 200):
+        out = _run(qkv, cu, 4, hw, cuda_device)
+        ref = O.attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu, hw, faithful=False)
+        got = out.cpu().float().view_as(ref)
+        assert bool(torch.isfinite(got).all())
+        rep = O.cosine_report(got.reshape(got.shape[0], -1), ref.reshape(ref.shape[0], -1))
+        # near-one-hot softmax rows: P's bf16 rounding decides ties, so compare directions
+        assert rep["min_token_cos"] > 0.995 and rep["mean_token_cos"] > 0.9995, (q_scale, hw, rep)
+
+
 @pytest.mark.parametrize("half_window", [None, 64])
 def test_no_cross_sequence_leakage(pe, cuda_device, half_window):
     # tests/test_packed_short_attention.py:110-124 of the reference
