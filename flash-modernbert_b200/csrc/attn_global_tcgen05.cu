@@ -48,7 +48,8 @@ constexpr uint32_t G_TMEM_COLS = 256;
 constexpr uint32_t G_S_COL = 0;    // S: columns 0..127
 constexpr uint32_t G_O_COL = 128;  // O: columns 128..191
 constexpr uint32_t G_P_COL = 192;  // P: bf16 pairs, keys 2c and 2c + 1 in column 192 + c
-constexpr float G_RESCALE_LOG2 = 8.0f;
+constexpr float G_RESCALE_LOG2 = 8.0f;  // drift of the maximum that moves the reference
+constexpr float G_REDO_LOG2 = 60.0f;    // drift at which a tile is redone against a new reference
 
 enum {
   GB_Q_FULL = 0,
@@ -135,6 +136,12 @@ __device__ __forceinline__ void g_tmem_ld8(uint32_t taddr, uint32_t* v) {
 __device__ __forceinline__ void g_tmem_st8(uint32_t taddr, const uint32_t* v) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
                "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+
+__device__ __forceinline__ void g_tmem_st4(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v[0]),
+               "r"(v[1]), "r"(v[2]), "r"(v[3])
                : "memory");
 }
 
@@ -369,8 +376,16 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         // Rows past the end of the sequence are computed like the others (on whatever TMA
         // fetched) and never stored: masking them would only make their warps diverge.
       }
-      float m_used = -INFINITY;  // the maximum P and the accumulator are scaled to
+      // P and the accumulator are scaled to 2^m_ref.  m_ref need not be the running maximum:
+      // fp32 and bf16 carry 8 exponent bits, so any reference within about 2^60 of the
+      // maximum gives the same relative precision.  A tile is therefore exponentiated against
+      // the reference it inherits while its own maximum is still being reduced (the two
+      // instruction streams interleave instead of running one after the other); the maximum
+      // moves the reference afterwards (pending) once it has drifted by more than 2^8.
+      float m_ref = 0.f;
       float l_run = 0.f;
+      float m_pend = 0.f;
+      bool pend = false;
 
       for (int j = 0; j < n_kv; ++j, ++g, col0 += G_BN) {
         wait(bar(GB_S_FULL), g & 1);
@@ -380,15 +395,20 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         g_tmem_ld32(lane_addr + G_S_COL + 32, sv + 32);
         g_tmem_ld32(lane_addr + G_S_COL + 64, sv + 64);
         g_tmem_ld32(lane_addr + G_S_COL + 96, sv + 96);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(GB_S_EMPTY));  // the next Q K^T may overwrite S now
-
         const int c_lo = key_lo - col0, c_hi = key_hi - col0;  // valid columns [c_lo, c_hi]
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
         // warp-uniform, so a warp never runs both branches
-        if (__all_sync(0xffffffffu, c_lo <= 0 && c_hi >= G_BN - 1)) {
+        const bool full = __all_sync(0xffffffffu, c_lo <= 0 && c_hi >= G_BN - 1);
+        if (__any_sync(0xffffffffu, pend)) {  // rare: move the reference up to the last tile's maximum
+          wait(bar(GB_O_FULL), (g - 1) & 1);  // its P V has retired (pend is never set when j == 0)
+          tc_fence_after();
+          const float alpha = pend ? g_ex2(m_ref - m_pend) : 1.0f;
+          g_rescale_accumulator(lane_addr + G_O_COL, alpha);
+          l_run *= alpha;
+          if (pend) m_ref = m_pend;
+        }
+        tmem_ld_wait();
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
+        if (full) {
 #pragma unroll
           for (int c = 0; c < 128; c += 2)
             mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
@@ -400,44 +420,81 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
             mx4[c & 3] = fmaxf(mx4[c & 3], v);
           }
         }
-        const float m_new = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-        if (j == 0) {
-          m_used = m_new;
-        } else {
-          // P is a single buffer and O an accumulator: the previous tile's P V must have retired
-          // before P is overwritten or O rescaled.  It was issued a whole max pass ago, so this
-          // wait is normally over at the first poll.
-          wait(bar(GB_O_FULL), (g - 1) & 1);
-          tc_fence_after();
-          // -inf + 8 stays -inf, so a row that has seen no valid key yet moves to any finite
-          // maximum; its accumulator and sum are still exactly zero and stay so (alpha = 0).
-          const bool grow = m_new > m_used + G_RESCALE_LOG2;
-          if (__any_sync(0xffffffffu, grow)) {
-            const float alpha = grow ? g_ex2(m_used - m_new) : 1.0f;
-            g_rescale_accumulator(lane_addr + G_O_COL, alpha);
-            l_run *= alpha;
-            if (grow) m_used = m_new;
-          }
-        }
-        const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c16 = 0; c16 < 8; ++c16) {  // 16 keys = 8 columns of bf16 pairs at a time
-          uint32_t pk[8];
+        auto exp16 = [&](int c16, uint32_t* pk) {  // 16 keys -> 8 bf16 pairs
 #pragma unroll
           for (int e = 0; e < 16; e += 2) {
-            const float p0 = g_ex2(fmaf(__uint_as_float(sv[c16 * 16 + e]), scale_log2, -m_safe));
-            const float p1 = g_ex2(fmaf(__uint_as_float(sv[c16 * 16 + e + 1]), scale_log2, -m_safe));
+            const float p0 = g_ex2(fmaf(__uint_as_float(sv[c16 * 16 + e]), scale_log2, -m_ref));
+            const float p1 = g_ex2(fmaf(__uint_as_float(sv[c16 * 16 + e + 1]), scale_log2, -m_ref));
             sum4[(e >> 1) & 3] += p0 + p1;
             pk[e >> 1] = pack_bf16(p0, p1);
           }
-          g_tmem_st8(lane_addr + G_P_COL + c16 * 8, pk);
+        };
+        // The first 32 keys are exponentiated in the same straight-line stretch as the maximum
+        // reduction above, before anything has to wait for the P buffer.
+        uint32_t pk0[8], pk1[8];
+        exp16(0, pk0);
+        exp16(1, pk1);
+        if (j > 0) {
+          // P is a single buffer and O an accumulator: the previous tile's P V must have retired
+          // before P is overwritten (or O rescaled, below).
+          wait(bar(GB_O_FULL), (g - 1) & 1);
+          tc_fence_after();
+        }
+        g_tmem_st8(lane_addr + G_P_COL, pk0);
+        g_tmem_st8(lane_addr + G_P_COL + 8, pk1);
+        const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+        // The tile's maximum is known while S is still ours.  If the inherited reference is more
+        // than 2^60 below it (or, for an item's first tile, above it), P would overflow (or
+        // vanish): move the reference to this maximum and redo the tile from S.
+        const bool bad = (m_tile > -INFINITY) &&
+                         (m_tile - m_ref > G_REDO_LOG2 || (j == 0 && m_ref - m_tile > G_REDO_LOG2));
+        if (__any_sync(0xffffffffu, bad)) {
+          if (j > 0) {
+            const float alpha = bad ? g_ex2(m_ref - m_tile) : 1.0f;
+            g_rescale_accumulator(lane_addr + G_O_COL, alpha);
+            l_run *= alpha;
+          }
+          if (bad) m_ref = m_tile;
+          sum4[0] = sum4[1] = sum4[2] = sum4[3] = 0.f;
+#pragma unroll 1
+          for (int c8 = 0; c8 < 16; ++c8) {
+            uint32_t v8[8], pk[4];
+            g_tmem_ld8(lane_addr + G_S_COL + c8 * 8, v8);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              const int c = c8 * 8 + e;
+              const float s0 = (full || (c >= c_lo && c <= c_hi)) ? __uint_as_float(v8[e]) : -INFINITY;
+              const float s1 = (full || (c + 1 >= c_lo && c + 1 <= c_hi)) ? __uint_as_float(v8[e + 1]) : -INFINITY;
+              const float p0 = g_ex2(fmaf(s0, scale_log2, -m_ref));
+              const float p1 = g_ex2(fmaf(s1, scale_log2, -m_ref));
+              sum4[(e >> 1) & 3] += p0 + p1;
+              pk[e >> 1] = pack_bf16(p0, p1);
+            }
+            g_tmem_st4(lane_addr + G_P_COL + c8 * 4, pk);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(GB_S_EMPTY));
+        } else {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(GB_S_EMPTY));  // the next Q K^T may overwrite S now
+#pragma unroll
+          for (int c16 = 2; c16 < 8; ++c16) {
+            uint32_t pk[8];
+            exp16(c16, pk);
+            g_tmem_st8(lane_addr + G_P_COL + c16 * 8, pk);
+          }
         }
         g_tmem_st_wait();
         l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(GB_P_FULL));
+        pend = m_tile > m_ref + G_RESCALE_LOG2;
+        m_pend = m_tile;
       }
       {  // the item's accumulator: normalise and store this row
         const GItem it = g_make_item(__ldg(tile_info + item / nh), item, nh, half_window);
