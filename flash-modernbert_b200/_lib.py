@@ -33,6 +33,7 @@ OPT_FUSED_ROPE = 2
 OPT_LOCAL_ATTN_SINGLE_PASS = 3
 OPT_FUSED_RESIDUAL = 4
 OPT_ATTN_TWO_CTA = 5
+OPT_LOCAL_ATTN_TWO_CTA = 6
 
 
 class NativeLibraryError(PackedEncodersError):

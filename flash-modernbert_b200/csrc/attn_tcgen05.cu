@@ -651,6 +651,8 @@ int attn_run_tc(const void* qkv, const int4* tile_info, const int32_t* total_til
   if (rc != PE_OK) return rc;
   const int64_t max_items = max_tiles * nh;
   const int grid = (int)(max_items < sm_count() ? max_items : sm_count());
+  if (half_window == TC_BN / 2 && get_option(OPT_LOCAL_ATTN_TWO_CTA))
+    return attn_run_local_tc2(qkv, tile_info, total_tiles, max_tiles, T, nh, out, status, st);
   // The single-pass kernel relies on the band being exactly one key tile wide.
   if (half_window == TC_BN / 2 && get_option(OPT_LOCAL_ATTN_SINGLE_PASS))
     attn_varlen_tc_kernel<true><<<grid, TC_THREADS, TC_SMEM, st>>>(

@@ -8,7 +8,7 @@ namespace pe {
 
 static int g_options[OPT_COUNT] = {0, /*OPT_FUSED_GEGLU*/ 1, /*OPT_FUSED_ROPE*/ 1,
                                    /*OPT_LOCAL_ATTN_SINGLE_PASS*/ 1, /*OPT_FUSED_RESIDUAL*/ 1,
-                                   /*OPT_ATTN_TWO_CTA*/ 1};
+                                   /*OPT_ATTN_TWO_CTA*/ 1, /*OPT_LOCAL_ATTN_TWO_CTA*/ 1};
 
 int get_option(int key) { return (key > 0 && key < OPT_COUNT) ? g_options[key] : 0; }
 

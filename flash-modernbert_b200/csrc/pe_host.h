@@ -53,10 +53,15 @@ int attn_run_tc(const void* qkv, const int4* tile_info, const int32_t* total_til
 int attn_run_global_tc(const void* qkv, const int4* tile_info, const int32_t* total_tiles,
                        int64_t max_tiles, int64_t T, int nh, int half_window, void* out,
                        int32_t* status, cudaStream_t st);
+// Sliding-window (half window 64) attention with two CTAs per SM, S / P / O in place in tensor memory.
+int attn_run_local_tc2(const void* qkv, const int4* tile_info, const int32_t* total_tiles,
+                       int64_t max_tiles, int64_t T, int nh, void* out, int32_t* status,
+                       cudaStream_t st);
 
 // Process-wide switches (pe_set_option).
 enum Option : int { OPT_FUSED_GEGLU = 1, OPT_FUSED_ROPE = 2, OPT_LOCAL_ATTN_SINGLE_PASS = 3,
-                    OPT_FUSED_RESIDUAL = 4, OPT_ATTN_TWO_CTA = 5, OPT_COUNT };
+                    OPT_FUSED_RESIDUAL = 4, OPT_ATTN_TWO_CTA = 5, OPT_LOCAL_ATTN_TWO_CTA = 6,
+                    OPT_COUNT };
 int get_option(int key);
 
 }  // namespace pe

@@ -90,6 +90,10 @@ int pe_device_check(void);
    that keeps two CTAs per SM and the output accumulator in tensor memory (1), or the
    one-CTA-per-SM kernel with eight softmax warps (0). */
 #define PE_OPT_ATTN_TWO_CTA 5
+/* key 6 (PE_OPT_LOCAL_ATTN_TWO_CTA, default 1): sliding-window layers (half window 64) of long
+   batches use the kernel that keeps two CTAs per SM and S, P and O in place in tensor memory (1),
+   or the one-CTA-per-SM kernels selected by key 3 (0). */
+#define PE_OPT_LOCAL_ATTN_TWO_CTA 6
 int pe_set_option(int key, int value);
 
 /* ---- padding boundary ------------------------------------------------------ */
