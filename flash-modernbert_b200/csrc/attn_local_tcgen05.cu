@@ -1,9 +1,10 @@
 // Sliding-window (|i - j| <= 64) varlen attention on the sm_100a tensor cores, two CTAs per SM.
 //
 // A 128-query tile attends a window of at most 256 keys (64 before its first query to 64 after
-// its last), so an item (query tile, head) is ONE pass: S = Q K^T for both 128-key tiles, the
-// exact row maxima, P = exp2(S - max), O = P V.  There is no running maximum to maintain and
-// nothing to rescale.  What limits such a kernel is latency: one softmax warp per scheduler
+// its last), so an item (query tile, head) is ONE pass: S = Q K^T for both 128-key tiles, a
+// reference exponent per row (the row maximum, or a cheaper bound within 2^60 above it),
+// P = exp2(S - reference), O = P V.  There is no running maximum to maintain and nothing to
+// rescale.  What limits such a kernel is latency: one softmax warp per scheduler
 // executes a long dependent instruction stream per item, and each item is a chain of TMA ->
 // MMA -> softmax -> MMA -> store.  So a CTA is kept small enough for two to share an SM
 // (192 threads, 113 KB of shared memory, 256 tensor-memory columns) and otherwise simple: a
@@ -250,33 +251,69 @@ attn_local_tc2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
       // three chunks, then two, per wait.
       uint32_t va[32], vb[32], vc[32];
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
+      // Chunks 0 and 4 of a warp are where its rows' windows begin and end: they are always
+      // handled with the two-sided column test (no separate code for the rare case that they are
+      // entirely valid); chunks 1..3 are entirely valid except where a sequence ends inside them.
+      // Keeping the number of code variants down matters: the unrolled loops are long enough to
+      // spill out of the instruction cache.
       auto fold = [&](const uint32_t* v, int k) {
         if (masked & (1u << k)) return;
-        if (mixed & (1u << k)) {
+        if (k == 0 || k == 4 || (mixed & (1u << k))) {
+          const int lo = c_lo - (c_first + k) * 32, hi = c_hi - (c_first + k) * 32;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = (c_first + k) * 32 + i;
-            mx4[i & 3] = fmaxf(mx4[i & 3], (col >= c_lo && col <= c_hi) ? __uint_as_float(v[i]) : -INFINITY);
-          }
+          for (int i = 0; i < 32; ++i)
+            mx4[i & 3] = fmaxf(mx4[i & 3], (i >= lo && i <= hi) ? __uint_as_float(v[i]) : -INFINITY);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; i += 2)
             mx4[(i >> 1) & 3] = fmax3(mx4[(i >> 1) & 3], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
         }
       };
-      // pass 1: the row maximum
-      g_tmem_ld32(s_addr, va);
-      g_tmem_ld32(s_addr + 32, vb);
-      g_tmem_ld32(s_addr + 64, vc);
-      tmem_ld_wait();
-      fold(va, 0);
-      g_tmem_ld32(s_addr + 96, va);
-      fold(vb, 1);
-      g_tmem_ld32(s_addr + 128, vb);
-      fold(vc, 2);
-      tmem_ld_wait();
-      fold(va, 3);
-      fold(vb, 4);
+      // pass 1: the row maximum - or any reference within 2^60 above it, which serves as well
+      // (P keeps its relative precision in bf16, the sums are fp32).  When chunks 1..3 are valid
+      // for every row of the warp, the unmasked maximum over all five chunks is such a reference
+      // unless chunk 0 or 4 holds an out-of-window score more than 2^60 above everything in
+      // chunks 1..3: then, and at the ends of a sequence, the exact masked maximum is taken.
+      bool have_m = false;
+      if (masked == 0 && (mixed & 0xeu) == 0) {
+        float e4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        auto raw = [&](const uint32_t* v, float* chain) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            chain[(i >> 1) & 3] = fmax3(chain[(i >> 1) & 3], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+        };
+        g_tmem_ld32(s_addr, va);
+        g_tmem_ld32(s_addr + 32, vb);
+        g_tmem_ld32(s_addr + 64, vc);
+        tmem_ld_wait();
+        raw(va, e4);
+        g_tmem_ld32(s_addr + 96, va);
+        raw(vb, mx4);
+        g_tmem_ld32(s_addr + 128, vb);
+        raw(vc, mx4);
+        tmem_ld_wait();
+        raw(va, mx4);
+        raw(vb, e4);
+        const float m_in = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float m_edge = fmaxf(fmaxf(e4[0], e4[1]), fmaxf(e4[2], e4[3]));
+        have_m = __all_sync(0xffffffffu, (m_edge - m_in) * scale_log2 <= 60.0f);
+        mx4[0] = fmaxf(m_in, m_edge);
+        if (!have_m) mx4[0] = mx4[1] = mx4[2] = mx4[3] = -INFINITY;
+      }
+      if (!have_m) {
+        g_tmem_ld32(s_addr, va);
+        g_tmem_ld32(s_addr + 32, vb);
+        g_tmem_ld32(s_addr + 64, vc);
+        tmem_ld_wait();
+        fold(va, 0);
+        g_tmem_ld32(s_addr + 96, va);
+        fold(vb, 1);
+        g_tmem_ld32(s_addr + 128, vb);
+        fold(vc, 2);
+        tmem_ld_wait();
+        fold(va, 3);
+        fold(vb, 4);
+      }
       const float m = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       const float m_safe = (m == -INFINITY) ? 0.f : m;  // a row with no valid key: P = 0 throughout
 
@@ -288,14 +325,14 @@ attn_local_tc2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
 #pragma unroll
           for (int i = 0; i < 16; ++i) pk[i] = 0u;
         } else {
-          const bool mix = (mixed & (1u << k)) != 0;
+          const bool mix = k == 0 || k == 4 || (mixed & (1u << k)) != 0;
+          const int lo = c_lo - (c_first + k) * 32, hi = c_hi - (c_first + k) * 32;
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const int col = (c_first + k) * 32 + i;
             float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
             if (mix) {
-              s0 = (col >= c_lo && col <= c_hi) ? s0 : -INFINITY;
-              s1 = (col + 1 >= c_lo && col + 1 <= c_hi) ? s1 : -INFINITY;
+              s0 = (i >= lo && i <= hi) ? s0 : -INFINITY;
+              s1 = (i + 1 >= lo && i + 1 <= hi) ? s1 : -INFINITY;
             }
             const float p0 = g_ex2(fmaf(s0, scale_log2, -m_safe));
             const float p1 = g_ex2(fmaf(s1, scale_log2, -m_safe));

@@ -93,7 +93,7 @@ def test_row_maximum_drifts_far_between_key_tiles(pe, cuda_device, q_scale):
     qkv[700:1000, 0] = (4.1 + 0.1 * torch.randn(300, 4, 64, generator=gen)).to(torch.bfloat16)
     qkv[700:828, 1] = (-4.1 + 0.1 * torch.randn(128, 4, 64, generator=gen)).to(torch.bfloat16)
     qkv[828:1000, 1] = (0.02 * torch.randn(172, 4, 64, generator=gen)).to(torch.bfloat16)
-    for hw in (None, 200):
+    for hw in (None, 200, 64):   # 64: the sliding-window kernel's exact-maximum fallback
         out = _run(qkv, cu, 4, hw, cuda_device)
         ref = O.attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu, hw, faithful=False)
         got = out.cpu().float().view_as(ref)
