@@ -251,24 +251,6 @@ attn_local_tc2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
       // three chunks, then two, per wait.
       uint32_t va[32], vb[32], vc[32];
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
-      // Chunks 0 and 4 of a warp are where its rows' windows begin and end: they are always
-      // handled with the two-sided column test (no separate code for the rare case that they are
-      // entirely valid); chunks 1..3 are entirely valid except where a sequence ends inside them.
-      // Keeping the number of code variants down matters: the unrolled loops are long enough to
-      // spill out of the instruction cache.
-      auto fold = [&](const uint32_t* v, int k) {
-        if (masked & (1u << k)) return;
-        if (k == 0 || k == 4 || (mixed & (1u << k))) {
-          const int lo = c_lo - (c_first + k) * 32, hi = c_hi - (c_first + k) * 32;
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            mx4[i & 3] = fmaxf(mx4[i & 3], (i >= lo && i <= hi) ? __uint_as_float(v[i]) : -INFINITY);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2)
-            mx4[(i >> 1) & 3] = fmax3(mx4[(i >> 1) & 3], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-        }
-      };
       // pass 1: the row maximum - or any reference within 2^60 above it, which serves as well
       // (P keeps its relative precision in bf16, the sums are fp32).  When chunks 1..3 are valid
       // for every row of the warp, the unmasked maximum over all five chunks is such a reference
@@ -301,41 +283,44 @@ attn_local_tc2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         if (!have_m) mx4[0] = mx4[1] = mx4[2] = mx4[3] = -INFINITY;
       }
       if (!have_m) {
-        g_tmem_ld32(s_addr, va);
-        g_tmem_ld32(s_addr + 32, vb);
-        g_tmem_ld32(s_addr + 64, vc);
-        tmem_ld_wait();
-        fold(va, 0);
-        g_tmem_ld32(s_addr + 96, va);
-        fold(vb, 1);
-        g_tmem_ld32(s_addr + 128, vb);
-        fold(vc, 2);
-        tmem_ld_wait();
-        fold(va, 3);
-        fold(vb, 4);
+        // Exact masked maximum: one copy of the code, rolled over the five chunks (a tensor-memory
+        // round trip each).  Unrolled variants of every rarely-taken path would push the hot loops
+        // out of the instruction cache.
+#pragma unroll 1
+        for (int k = 0; k < 5; ++k) {
+          if (masked & (1u << k)) continue;
+          g_tmem_ld32(s_addr + k * 32, va);
+          tmem_ld_wait();
+          const int lo = c_lo - (c_first + k) * 32, hi = c_hi - (c_first + k) * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            mx4[i & 3] = fmaxf(mx4[i & 3], (i >= lo && i <= hi) ? __uint_as_float(va[i]) : -INFINITY);
+        }
       }
       const float m = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       const float m_safe = (m == -INFINITY) ? 0.f : m;  // a row with no valid key: P = 0 throughout
 
       // pass 2: P = exp2(S * scale - m) as bf16 pairs, chunk c of S into the 16 columns at 16 c
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      auto emit = [&](const uint32_t* v, int k) {
+      // Chunks 0 and 4 of a warp are where its rows' windows begin and end: they are always
+      // masked with the two-sided column test; chunks 1..3 only where a sequence ends inside them.
+      // The masking is a block of its own in front of one common exponentiation block.
+      auto emit = [&](uint32_t* v, int k) {
         uint32_t pk[16];
         if (masked & (1u << k)) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) pk[i] = 0u;
         } else {
-          const bool mix = k == 0 || k == 4 || (mixed & (1u << k)) != 0;
-          const int lo = c_lo - (c_first + k) * 32, hi = c_hi - (c_first + k) * 32;
+          if (k == 0 || k == 4 || (mixed & (1u << k)) != 0) {
+            const int lo = c_lo - (c_first + k) * 32, hi = c_hi - (c_first + k) * 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              v[i] = (i >= lo && i <= hi) ? v[i] : 0xff800000u;  // -inf
+          }
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-            if (mix) {
-              s0 = (i >= lo && i <= hi) ? s0 : -INFINITY;
-              s1 = (i + 1 >= lo && i + 1 <= hi) ? s1 : -INFINITY;
-            }
-            const float p0 = g_ex2(fmaf(s0, scale_log2, -m_safe));
-            const float p1 = g_ex2(fmaf(s1, scale_log2, -m_safe));
+            const float p0 = g_ex2(fmaf(__uint_as_float(v[i]), scale_log2, -m_safe));
+            const float p1 = g_ex2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -m_safe));
             sum4[(i >> 1) & 3] += p0 + p1;
             pk[i >> 1] = pack_bf16(p0, p1);
           }
