@@ -354,41 +354,19 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         tmem_ld_wait();
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
         // A tile that is not valid for every row of the warp (the last one of a sequence, every
-        // one of a band) is handled in groups of 16 columns, each classified for the whole warp:
-        // all valid (as in a full tile), all masked (skipped: P = 0 and no exp2 at all - three
-        // eighths of a 64-wide band's two tiles), or mixed (masked element by element).
-        uint32_t skip = 0;  // bit c16: columns [16 c16, 16 c16 + 16) are masked for the whole warp
-        if (full) {
+        // one of a band) first has its invalid scores replaced by -inf, in one block of its own;
+        // the maximum and the exponentials below are then the same code for every tile.  (Separate
+        // unrolled variants per 16-column group were 1 % faster on bands and cost more than that
+        // on full attention by crowding the instruction cache.)
+        if (!full) {
 #pragma unroll
-          for (int c = 0; c < 128; c += 2)
-            mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
-        } else {
-#pragma unroll
-          for (int c16 = 0; c16 < 8; ++c16) {
-            const int lo = c16 * 16, hi = lo + 15;
-            if (__all_sync(0xffffffffu, c_hi < lo || c_lo > hi)) {
-              skip |= 1u << c16;
-            } else if (__all_sync(0xffffffffu, c_lo <= lo && c_hi >= hi)) {
-#pragma unroll
-              for (int c = lo; c < lo + 16; c += 2)
-                mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
-            } else {
-#pragma unroll
-              for (int c = lo; c < lo + 16; ++c) {
-                const float v = (c >= c_lo && c <= c_hi) ? __uint_as_float(sv[c]) : -INFINITY;
-                sv[c] = __float_as_uint(v);
-                mx4[c & 3] = fmaxf(mx4[c & 3], v);
-              }
-            }
-          }
+          for (int c = 0; c < 128; ++c) sv[c] = (c >= c_lo && c <= c_hi) ? sv[c] : 0xff800000u;  // -inf
         }
+#pragma unroll
+        for (int c = 0; c < 128; c += 2)
+          mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         auto exp16 = [&](int c16, uint32_t* pk) {  // 16 keys -> 8 bf16 pairs
-          if (skip & (1u << c16)) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) pk[e] = 0u;
-            return;
-          }
 #pragma unroll
           for (int e = 0; e < 16; e += 2) {
             const float p0 = g_ex2(fmaf(__uint_as_float(sv[c16 * 16 + e]), scale_log2, -m_ref));
