@@ -343,7 +343,7 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         const int c_lo = key_lo - col0, c_hi = key_hi - col0;  // valid columns [c_lo, c_hi]
         // warp-uniform, so a warp never runs both branches
         const bool full = __all_sync(0xffffffffu, c_lo <= 0 && c_hi >= G_BN - 1);
-        if (__any_sync(0xffffffffu, pend)) {  // rare: move the reference up to the last tile's maximum
+        if (__builtin_expect(__any_sync(0xffffffffu, pend), 0)) {  // rare: move the reference up to the last tile's maximum
           wait(bar(GB_O_FULL), (g - 1) & 1);  // its P V has retired (pend is never set when j == 0)
           tc_fence_after();
           const float alpha = pend ? g_ex2(m_ref - m_pend) : 1.0f;
@@ -358,7 +358,7 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         // the maximum and the exponentials below are then the same code for every tile.  (Separate
         // unrolled variants per 16-column group were 1 % faster on bands and cost more than that
         // on full attention by crowding the instruction cache.)
-        if (!full) {
+        if (__builtin_expect(!full, 0)) {
 #pragma unroll
           for (int c = 0; c < 128; ++c) sv[c] = (c >= c_lo && c <= c_hi) ? sv[c] : 0xff800000u;  // -inf
         }
@@ -394,7 +394,7 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         // vanish): move the reference to this maximum and redo the tile from S.
         const bool bad = (m_tile > -INFINITY) &&
                          (m_tile - m_ref > G_REDO_LOG2 || (j == 0 && m_ref - m_tile > G_REDO_LOG2));
-        if (__any_sync(0xffffffffu, bad)) {
+        if (__builtin_expect(__any_sync(0xffffffffu, bad), 0)) {
           if (j > 0) {
             const float alpha = bad ? g_ex2(m_ref - m_tile) : 1.0f;
             g_rescale_accumulator(lane_addr + G_O_COL, alpha);

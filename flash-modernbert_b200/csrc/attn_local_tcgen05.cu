@@ -282,7 +282,7 @@ attn_local_tc2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         mx4[0] = fmaxf(m_in, m_edge);
         if (!have_m) mx4[0] = mx4[1] = mx4[2] = mx4[3] = -INFINITY;
       }
-      if (!have_m) {
+      if (__builtin_expect(!have_m, 0)) {
         // Exact masked maximum: one copy of the code, rolled over the five chunks (a tensor-memory
         // round trip each).  Unrolled variants of every rarely-taken path would push the hot loops
         // out of the instruction cache.
