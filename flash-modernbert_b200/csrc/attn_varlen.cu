@@ -334,6 +334,7 @@ int attn_pick_bm(int max_seqlen) {
 
 // Scratch layout: tile_start int32[n_seqs + 1], padded to 16 bytes, then tile_info int4[max tiles].
 static size_t info_offset(int n_seqs) { return (size_t(n_seqs + 2) * sizeof(int32_t) + 15) & ~size_t(15); }
+size_t attn_info_offset(int n_seqs) { return info_offset(n_seqs); }
 
 size_t attn_scratch_bytes(int64_t T, int n_seqs) {
   return info_offset(n_seqs) + size_t(T / 16 + n_seqs + 1) * sizeof(int4);

@@ -43,6 +43,8 @@ int make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
 // reuses it for every layer (attn_varlen.cu).  `scratch` holds pe_attn_workspace_bytes.
 int attn_pick_bm(int max_seqlen);
 size_t attn_scratch_bytes(int64_t T, int n_seqs);
+// Byte offset of the int4 tile descriptors inside that scratch (tile_start int32[n_seqs + 1] comes first).
+size_t attn_info_offset(int n_seqs);
 int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int bm, void* scratch, cudaStream_t st);
 int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh, int half_window,
              int bm, void* out, int32_t* status, cudaStream_t st);

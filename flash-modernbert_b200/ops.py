@@ -234,3 +234,27 @@ def attention_varlen_qkv_static(qkv: Tensor, cu_seqlens: Tensor, max_seqlen: int
                                                status_word(qkv.device).data_ptr(), c.stream),
                    "pe_attn_varlen_static")
     return out
+
+
+def pool_packed(hidden: Tensor, cu_seqlens: Tensor, mode: str = "mean", normalize: bool = True) -> Tensor:
+    """Sentence embeddings from the packed last hidden state, as the reference's callers compute
+    them right after `packed_forward` (benchmarks/showcases/inference.py:193-206): per sequence
+    the fp32 mean of its token rows (`mode="mean"`) or its first token (`mode="cls"`),
+    optionally L2-normalised like `F.normalize`, rounded to bf16 last. `[T, H]` -> `[N, H]`."""
+    if mode not in ("mean", "cls"):
+        raise ValueError(f"pool_packed: mode must be 'mean' or 'cls', got {mode!r}")
+    hidden = _bf16_cuda(hidden, "hidden")
+    total, width = hidden.shape
+    cu = cu_seqlens.contiguous()
+    if cu.dtype != torch.int32:
+        raise TypeError("pool_packed: cu_seqlens must be int32")
+    n_seqs = cu.numel() - 1
+    out = torch.empty(n_seqs, width, dtype=torch.bfloat16, device=hidden.device)
+    with _Call(hidden) as c:
+        ws_bytes = int(c.lib.pe_pool_workspace_bytes(total, n_seqs, width)) if mode == "mean" else 0
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=hidden.device)
+        _lib.check(c.lib.pe_pool_packed(hidden.data_ptr(), cu.data_ptr(), n_seqs, total, width,
+                                        1 if mode == "mean" else 0, 1 if normalize else 0,
+                                        out.data_ptr(), ws.data_ptr(), ws_bytes, c.stream),
+                   "pe_pool_packed")
+    return out

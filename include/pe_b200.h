@@ -182,6 +182,22 @@ int pe_gemm_qkv_rope_bf16(const void* A, const void* Wqkv, void* qkv, int64_t M,
 int pe_gemm_residual_bf16(const void* A, const void* W, const void* X, void* C, int64_t M, int Nout,
                           int K, int32_t* status, void* stream);
 
+/* ---- pooling head on the packed output ---------------------------------------- */
+
+/* Bytes of workspace pe_pool_packed needs for mean pooling (mode 1); mode 0 needs none. */
+size_t pe_pool_workspace_bytes(int64_t T, int n_seqs, int H);
+
+/* benchmarks/showcases/inference.py:193-206 (what the reference's callers do with the output of
+ * packed_forward): per sequence, the fp32 sum of its token rows divided by its length (mode 1)
+ * or its first token's row (mode 0); normalize != 0 divides by max(||x||_2, 1e-12) as
+ * F.normalize does; the result is rounded to bf16 last.
+ * hidden: bf16 [T, H]; cu_seqlens: int32 [n_seqs + 1]; out: bf16 [n_seqs, H]; zero-length
+ * sequences give zero rows.  H a multiple of 8, at most 2048.  Summation order is fixed
+ * (no atomics): repeated calls are bit-identical. */
+int pe_pool_packed(const void* hidden, const int32_t* cu_seqlens, int n_seqs, int64_t T, int H,
+                   int mode, int normalize, void* out, void* workspace, size_t workspace_bytes,
+                   void* stream);
+
 /* ---- attention -------------------------------------------------------------- */
 
 /* Bytes of scratch pe_attn_varlen needs for n_seqs sequences and T tokens. */

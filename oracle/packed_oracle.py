@@ -248,6 +248,27 @@ def hf_eager_padded(model, input_ids: Tensor, attention_mask: Tensor) -> Tensor:
     return model(input_ids=input_ids, attention_mask=attention_mask).last_hidden_state
 
 
+def pool(hidden: Tensor, cu_seqlens, mode: str = "mean", normalize: bool = True) -> Tensor:
+    """Sentence embeddings from a packed hidden state, following
+    benchmarks/showcases/inference.py:193-206 of the reference: segment sums in fp32
+    (`index_add_` of `hidden.float()`), divided by the lengths, `F.normalize(p=2, dim=-1)`
+    (eps 1e-12), cast to the hidden state's dtype last. `mode="cls"` takes the first token of
+    each sequence instead of the mean. Zero-length sequences give zero rows."""
+    cu = [int(v) for v in cu_seqlens]
+    rows = []
+    for b, e in zip(cu[:-1], cu[1:]):
+        if e == b:
+            rows.append(torch.zeros(hidden.shape[-1], dtype=torch.float32))
+        elif mode == "cls":
+            rows.append(hidden[b].float())
+        else:
+            rows.append(hidden[b:e].float().sum(0) / float(e - b))
+    pooled = torch.stack(rows) if rows else torch.zeros(0, hidden.shape[-1])
+    if normalize:
+        pooled = torch.nn.functional.normalize(pooled, p=2, dim=-1)
+    return pooled.to(hidden.dtype)
+
+
 def cosine_report(actual: Tensor, expected: Tensor) -> dict:
     """Per-token and flat cosine, and max-abs error, between two [T, H] tensors."""
     a, e = actual.float(), expected.float()

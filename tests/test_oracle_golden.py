@@ -142,3 +142,29 @@ def test_attention_window_and_isolation():
     assert torch.equal(O.attention(q, k, v, cu, 64), O.attention(q, k, v, cu, None))
     far = O.attention(q, k, v, cu, 3)
     assert not torch.equal(far, base)
+
+
+def test_pool_oracle_known_answers():
+    """`oracle.pool` restates benchmarks/showcases/inference.py:193-206: segment mean in fp32,
+    F.normalize, cast last."""
+    import torch
+
+    from oracle import packed_oracle as O
+
+    hidden = torch.tensor([[3.0, 4.0], [1.0, 0.0], [3.0, 0.0], [0.0, 2.0]], dtype=torch.bfloat16)
+    cu = [0, 1, 3, 3, 4]
+    mean = O.pool(hidden, cu, "mean", False).float()
+    assert mean.tolist() == [[3.0, 4.0], [2.0, 0.0], [0.0, 0.0], [0.0, 2.0]]
+    unit = O.pool(hidden, cu, "mean", True).float()
+    assert torch.allclose(unit, torch.tensor([[0.6, 0.8], [1.0, 0.0], [0.0, 0.0], [0.0, 1.0]]), atol=4e-3)
+    cls = O.pool(hidden, cu, "cls", False).float()
+    assert cls.tolist() == [[3.0, 4.0], [1.0, 0.0], [0.0, 0.0], [0.0, 2.0]]
+    # against the reference's own formulation (index_add_ over repeat_interleave segments)
+    gen = torch.Generator().manual_seed(0)
+    h = torch.randn(37, 16, generator=gen).to(torch.bfloat16)
+    lens = torch.tensor([5, 20, 12])
+    seg = torch.repeat_interleave(torch.arange(3), lens)
+    sums = torch.zeros(3, 16).index_add_(0, seg, h.float())
+    ref = torch.nn.functional.normalize(sums / lens.unsqueeze(1).float(), p=2, dim=-1).to(torch.bfloat16)
+    got = O.pool(h, [0, 5, 25, 37], "mean", True)
+    assert float((got.float() - ref.float()).abs().max()) <= 2.0 ** -8
