@@ -1,3 +1,7 @@
+// The one-CTA-per-SM varlen attention kernels: the first tensor-core generation of this
+// library, kept selectable (pe_set_option keys 5 and 6) as a cross-check for the two-CTA kernels
+// in attn_global_tcgen05.cu and attn_local_tcgen05.cu, which the forward uses by default.
+//
 // Varlen attention for sequences longer than one short tile, on the sm_100a tensor
 // cores: S = Q K^T and O = P V run as tcgen05.mma with S and O in tensor memory,
 // Q / K / V tiles arrive by TMA straight from the fused qkv [T, 3*nh*64].

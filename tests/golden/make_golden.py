@@ -1,7 +1,7 @@
-"""Generates the golden fixtures in this directory. Run where the reference checkout is
-mounted (it is imported from REFERENCE_ROOT, default /root/reference):
+"""Generates the golden fixtures in this directory. Run where a checkout of the reference
+(pau-mensa/flash-modernbert) is available; it is imported from the directory REFERENCE_ROOT names:
 
-    python tests/golden/make_golden.py
+    REFERENCE_ROOT=<checkout of the reference> python tests/golden/make_golden.py
 
 Fixtures (all small .npz files, committed):
   unpad_cases.npz     outputs of the reference's own _unpad / _repad
@@ -25,7 +25,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT")
+if not REFERENCE_ROOT or not Path(REFERENCE_ROOT, "packed_encoders").is_dir():
+    raise SystemExit("set REFERENCE_ROOT to a checkout of the reference (the directory that holds packed_encoders/)")
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, REFERENCE_ROOT)
 

@@ -150,3 +150,22 @@ def test_full_size_properties(pe, cuda_device):
     const_v[:, 2] = 0.5
     out = ops.attention_varlen_qkv(const_v.view(total, -1), cu.to(cuda_device), max(lengths), 12, 64)
     assert float((out.float() - 0.5).abs().max()) < 4e-3
+
+
+@pytest.mark.parametrize("half_window,key", [(None, 5), (64, 6)])
+def test_one_cta_kernels_behind_their_options_agree(pe, cuda_device, half_window, key):
+    """`pe_set_option(5, 0)` / `(6, 0)` select the one-CTA-per-SM kernels; both generations must
+    agree with the reference and with each other to within P's bf16 rounding."""
+    from flash_modernbert_b200 import _lib
+
+    qkv, cu = _qkv([700, 129, 300, 2048], 4, cuda_device, seed=7)
+    lib = _lib.load()
+    new = _run(qkv, cu, 4, half_window, cuda_device)
+    try:
+        assert lib.pe_set_option(key, 0) == 0
+        old = _run(qkv, cu, 4, half_window, cuda_device)
+    finally:
+        lib.pe_set_option(key, 1)
+    _check(old, qkv, cu, half_window, f"one-CTA kernel, window={half_window}")
+    _check(new, qkv, cu, half_window, f"two-CTA kernel, window={half_window}")
+    assert float((old.float() - new.float()).abs().max()) < 0.02
