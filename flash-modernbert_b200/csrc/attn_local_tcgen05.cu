@@ -225,22 +225,35 @@ attn_local_tc2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
     // five 32-column chunks w .. w + 4 and writes P = 0 for the other three.
     const int c_first = warp;
     uint32_t n = 0;
-    int4 info = __ldg(tile_info + blockIdx.x / nh);
+    // (query tile, head) of the item, advanced by the stride without a division per item
+    int tile = blockIdx.x / nh, head = blockIdx.x % nh;
+    const int stride_tiles = stride_items / nh, stride_heads = stride_items % nh;
+    int4 info = __ldg(tile_info + tile);
     for (int item = blockIdx.x; item < total_items; item += stride_items, ++n) {
-      const int seq_begin = info.x, len = info.y, q0 = info.z, head = item % nh;
+      const int seq_begin = info.x, len = info.y, q0 = info.z;
+      const int this_head = head;
+      tile += stride_tiles;
+      head += stride_heads;
+      if (head >= nh) {
+        head -= nh;
+        ++tile;
+      }
       if (item + stride_items < total_items)  // next item's descriptor, in flight during this one
-        info = __ldg(tile_info + (item + stride_items) / nh);
+        info = __ldg(tile_info + tile);
       const int qi = q0 + row;  // position in the sequence
       // valid columns [c_lo, c_hi] of the 256-key window that starts at key q0 - 64
       const int c_lo = max(0, qi - LW_HALF_WINDOW) - (q0 - LW_HALF_WINDOW);
       const int c_hi = min(len - 1, qi + LW_HALF_WINDOW) - (q0 - LW_HALF_WINDOW);
       // the five chunks, classified for the whole warp: bit k set = chunk c_first + k
-      uint32_t masked = 0, mixed = 0;
+      uint32_t masked = 0, mixed = 0x11u;  // away from the ends of a sequence: chunks 0 and 4 are mixed
+      if (q0 < LW_HALF_WINDOW || q0 + 128 + LW_HALF_WINDOW > len) {  // the window leaves the sequence
+        mixed = 0;
 #pragma unroll
-      for (int k = 0; k < 5; ++k) {
-        const int lo = (c_first + k) * 32, hi = lo + 31;
-        if (__all_sync(0xffffffffu, c_hi < lo || c_lo > hi)) masked |= 1u << k;
-        else if (!__all_sync(0xffffffffu, c_lo <= lo && c_hi >= hi)) mixed |= 1u << k;
+        for (int k = 0; k < 5; ++k) {
+          const int lo = (c_first + k) * 32, hi = lo + 31;
+          if (__all_sync(0xffffffffu, c_hi < lo || c_lo > hi)) masked |= 1u << k;
+          else if (!__all_sync(0xffffffffu, c_lo <= lo && c_hi >= hi)) mixed |= 1u << k;
+        }
       }
       const uint32_t s_addr = lane_addr + c_first * 32;  // chunk k of this warp at + 32 k
 
@@ -384,7 +397,7 @@ attn_local_tc2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
       __syncwarp();
       {
         const int rows_valid = len - (q0 + warp * 32);  // rows of this warp inside the sequence
-        __nv_bfloat16* obase = out + (int64_t(seq_begin) + q0 + warp * 32) * H + head * 64 + (lane & 7) * 8;
+        __nv_bfloat16* obase = out + (int64_t(seq_begin) + q0 + warp * 32) * H + this_head * 64 + (lane & 7) * 8;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int r = i * 4 + (lane >> 3);
