@@ -100,6 +100,7 @@ PROTOTYPES = {
                                       c_void_p, c_int, c_void_p, c_void_p]),
     "pe_gemm_residual_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                       c_void_p, c_void_p]),
+    "pe_gemm_l2norm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "pe_pool_workspace_bytes": (c_size_t, [c_int64, c_int, c_int]),
     "pe_pool_packed": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p,
                                c_size_t, c_void_p]),

@@ -40,7 +40,7 @@ __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
-enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2, GEMM_RESIDUAL = 3 };
+enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2, GEMM_RESIDUAL = 3, GEMM_L2NORM = 4 };
 
 // Extra operands of the Wqkv + RoPE epilogue and of the residual epilogue.
 struct RopeArgs {
@@ -333,6 +333,37 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ob ^= 1u;
         }
         res_ready = res_chain;
+      } else if constexpr (MODE == GEMM_L2NORM) {
+        // Projection head: at most 256 output columns, so the tile holds whole rows and each
+        // thread can L2-normalise its own.  Two passes over the accumulator: the norm of the
+        // bf16-rounded row (rounded to bf16 itself, as a bf16 F.normalize produces it), then
+        // row / norm.
+        float ss = 0.f;
+        for (int c = 0; c * 64 < n_out; ++c) {
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32(t_addr + c * 64, lo);
+          tmem_ld_32x32(t_addr + c * 64 + 32, hi);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float a = round_bf16(__uint_as_float(lo[i])), b = round_bf16(__uint_as_float(hi[i]));
+            ss = fmaf(a, a, ss);
+            ss = fmaf(b, b, ss);
+          }
+        }
+        const float norm = fmaxf(round_bf16(sqrtf(ss)), 1e-12f);
+        for (int c = 0; c * 64 < n_out; ++c) {
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32(t_addr + c * 64, lo);
+          tmem_ld_32x32(t_addr + c * 64 + 32, hi);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            lo[i] = __float_as_uint(round_bf16(__uint_as_float(lo[i])) / norm);
+            hi[i] = __float_as_uint(round_bf16(__uint_as_float(hi[i])) / norm);
+          }
+          emit64(lo, hi, c * 64, row0);
+        }
       } else if constexpr (!GEGLU) {
         const int col0 = nt * BN;
 #pragma unroll 1
@@ -474,4 +505,15 @@ extern "C" int pe_gemm_residual_bf16(const void* A, const void* W, const void* X
   args.residual = static_cast<const __nv_bfloat16*>(X);
   return pe::launch_gemm<pe::GEMM_RESIDUAL>(A, W, C, M, Nout, K, Nout, 0, args, status,
                                             static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int pe_gemm_l2norm_bf16(const void* A, const void* W, void* C, int64_t M, int Nout, int K,
+                                   int32_t* status, void* stream) {
+  if (M == 0) return PE_OK;
+  int rc = pe::check_gemm_args(A, W, C, M, Nout, K, "pe_gemm_l2norm_bf16");
+  if (rc != PE_OK) return rc;
+  PE_REQUIRE(Nout <= pe::BN, "pe_gemm_l2norm_bf16: at most %d output columns (one tile holds whole rows), got %d",
+             pe::BN, Nout);
+  return pe::launch_gemm<pe::GEMM_L2NORM>(A, W, C, M, Nout, K, Nout, 0, pe::RopeArgs{}, status,
+                                          static_cast<cudaStream_t>(stream));
 }

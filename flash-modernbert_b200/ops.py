@@ -258,3 +258,21 @@ def pool_packed(hidden: Tensor, cu_seqlens: Tensor, mode: str = "mean", normaliz
                                         out.data_ptr(), ws.data_ptr(), ws_bytes, c.stream),
                    "pe_pool_packed")
     return out
+
+
+def project_normalize(hidden: Tensor, weight: Tensor) -> Tensor:
+    """Token-level projection head: `F.normalize(F.linear(hidden, weight), p=2, dim=-1)` in one
+    kernel, as the reference's ColBERT indexing path computes it after `packed_forward`
+    (benchmarks/helpers/packed_index.py:182-186). `weight` is `[out_features <= 256, H]`."""
+    hidden = _bf16_cuda(hidden, "hidden")
+    weight = _bf16_cuda(weight, "weight")
+    flat = hidden.reshape(-1, hidden.shape[-1])
+    if weight.shape[0] > 256:
+        raise ValueError("project_normalize: at most 256 output features (one tile holds whole rows)")
+    out = torch.empty(flat.shape[0], weight.shape[0], dtype=torch.bfloat16, device=hidden.device)
+    with _Call(hidden) as c:
+        _lib.check(c.lib.pe_gemm_l2norm_bf16(flat.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                                             flat.shape[0], weight.shape[0], weight.shape[1],
+                                             status_word(hidden.device).data_ptr(), c.stream),
+                   "pe_gemm_l2norm_bf16")
+    return out.view(*hidden.shape[:-1], weight.shape[0])

@@ -182,6 +182,15 @@ int pe_gemm_qkv_rope_bf16(const void* A, const void* Wqkv, void* qkv, int64_t M,
 int pe_gemm_residual_bf16(const void* A, const void* W, const void* X, void* C, int64_t M, int Nout,
                           int K, int32_t* status, void* stream);
 
+/* Projection head with per-token L2 normalisation, in one kernel
+ * (benchmarks/helpers/packed_index.py:182-186 of the reference: the ColBERT Dense projection of
+ * the token embeddings followed by F.normalize(p=2, dim=-1)):
+ * C[m, :] = y / max(bf16(||y||_2), 1e-12) with y = bf16(A[m, :] W^T), rounded to bf16.
+ * A: bf16 [M, K]; W: bf16 [Nout, K] (nn.Linear layout, no bias); C: bf16 [M, Nout];
+ * Nout <= 256 (a tile then holds whole rows), Nout and K multiples of 8. */
+int pe_gemm_l2norm_bf16(const void* A, const void* W, void* C, int64_t M, int Nout, int K,
+                        int32_t* status, void* stream);
+
 /* ---- pooling head on the packed output ---------------------------------------- */
 
 /* Bytes of workspace pe_pool_packed needs for mean pooling (mode 1); mode 0 needs none. */

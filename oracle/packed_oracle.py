@@ -269,6 +269,14 @@ def pool(hidden: Tensor, cu_seqlens, mode: str = "mean", normalize: bool = True)
     return pooled.to(hidden.dtype)
 
 
+def project_normalize(hidden: Tensor, weight: Tensor) -> Tensor:
+    """ColBERT-style token head, following benchmarks/helpers/packed_index.py:182-186 of the
+    reference: a bias-free Dense projection of the token embeddings (computed and stored in the
+    hidden state's dtype) followed by `F.normalize(p=2, dim=-1)` on that tensor."""
+    y = (hidden.float() @ weight.float().t()).to(hidden.dtype)
+    return torch.nn.functional.normalize(y, p=2, dim=-1)
+
+
 def cosine_report(actual: Tensor, expected: Tensor) -> dict:
     """Per-token and flat cosine, and max-abs error, between two [T, H] tensors."""
     a, e = actual.float(), expected.float()

@@ -73,3 +73,23 @@ def test_pool_full_size(pe, cuda_device):
         s, e = int(cu[n]), int(cu[n + 1])
         ref = torch.nn.functional.normalize(rnd[s:e].float().mean(0), dim=-1)
         assert float((out[n].float() - ref).abs().max()) < 2e-3
+
+
+@pytest.mark.parametrize("out_features", [128, 96, 256])
+@pytest.mark.parametrize("rows", [1, 130, 5000])
+def test_project_normalize_against_oracle(pe, cuda_device, out_features, rows):
+    """`pe_gemm_l2norm_bf16`: Dense projection + per-token L2 normalisation in one kernel, against
+    the oracle's restatement of benchmarks/helpers/packed_index.py:182-186."""
+    from flash_modernbert_b200 import ops
+
+    gen = torch.Generator().manual_seed(3)
+    hidden = torch.randn(rows, 768, generator=gen).to(torch.bfloat16)
+    weight = (torch.randn(out_features, 768, generator=gen) * 0.03).to(torch.bfloat16)
+    got = ops.project_normalize(hidden.to(cuda_device), weight.to(cuda_device)).cpu().float()
+    ref = O.project_normalize(hidden, weight).float()
+    assert got.shape == ref.shape == (rows, out_features)
+    # unit rows; elements within two bf16 steps (the fp32 sums run in a different order)
+    assert float((got.norm(dim=-1) - 1).abs().max()) < 6e-3
+    assert float((got - ref).abs().max()) <= 2.0 ** -7
+    rep = O.cosine_report(got, ref)
+    assert rep["min_token_cos"] > 0.9999, rep

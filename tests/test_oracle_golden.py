@@ -168,3 +168,15 @@ def test_pool_oracle_known_answers():
     ref = torch.nn.functional.normalize(sums / lens.unsqueeze(1).float(), p=2, dim=-1).to(torch.bfloat16)
     got = O.pool(h, [0, 5, 25, 37], "mean", True)
     assert float((got.float() - ref.float()).abs().max()) <= 2.0 ** -8
+
+
+def test_project_normalize_oracle_known_answer():
+    import torch
+
+    from oracle import packed_oracle as O
+
+    hidden = torch.tensor([[1.0, 2.0], [0.0, 0.0]], dtype=torch.bfloat16)
+    weight = torch.tensor([[3.0, 0.0], [0.0, 2.0]], dtype=torch.bfloat16)
+    out = O.project_normalize(hidden, weight).float()
+    assert torch.allclose(out[0], torch.tensor([0.6, 0.8]), atol=4e-3)
+    assert out[1].tolist() == [0.0, 0.0]          # zero row: divided by eps, stays zero
