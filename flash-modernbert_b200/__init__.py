@@ -13,7 +13,7 @@ sm_100a CUDA behind a C ABI, include/pe_b200.h); there is no fallback path.
 """
 from __future__ import annotations
 
-from .collate import PackedBatch, pack_sequences
+from .collate import PackedBatch, encode_in_batches, pack_sequences, token_budget_batches
 from .config import ModernBertParams
 from .errors import PackedEncodersError, UnsupportedTargetError, ValidationError
 from .forward import fused_forward, packed_forward
@@ -39,6 +39,8 @@ __all__ = [
     "find_encoder",
     "pack_sequences",
     "PackedBatch",
+    "token_budget_batches",
+    "encode_in_batches",
     "PackedEncodersError",
     "UnsupportedTargetError",
     "ValidationError",

@@ -328,3 +328,29 @@ def test_cfg2_queries_through_token_bucket_graphs(pe, cuda_device, base_models):
         assert O.cosine_report(got.cpu(), ref)["min_token_cos"] >= COS_GATE
     finally:
         pe.unpack(gpu)
+
+
+def test_encode_in_token_budget_batches(pe, cuda_device, tiny_models):
+    """`encode_in_batches` (the loop of benchmarks/showcases/inference.py:186-209): the same
+    embeddings whether the corpus goes through in one batch or in token-budget micro-batches,
+    returned in the callers' order."""
+    _, _, gpu, vocab = tiny_models
+    wl = S.workload("tiny_mixed", vocab)
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    bounds = np.concatenate([[0], np.cumsum(wl.lengths)])
+    seqs = [wl.ids[bounds[i]:bounds[i + 1]] for i in range(len(wl.lengths))]
+    whole = pe.encode_in_batches(gpu, params, seqs, 10 ** 9, sort_by_length=False)
+    budget = max(wl.lengths) + 8                      # forces several micro-batches
+    assert len(pe.token_budget_batches(wl.lengths, budget)) > 2
+    split = pe.encode_in_batches(gpu, params, seqs, budget)
+    assert whole.shape == split.shape == (len(seqs), 256)
+    # per-sequence results do not depend on what else is in the batch
+    assert float((whole.float() - split.float()).abs().max()) <= 2.0 ** -7
+    assert float((split.float().norm(dim=-1) - 1).abs().max()) < 6e-3
+    # pool=None: per-sequence hidden states, identical rows to one packed forward
+    ids, cu, max_s, pos = _packed_inputs(wl, cuda_device)
+    ref = pe.packed_forward(gpu, params, ids, cu, max_s, pos)
+    parts = pe.encode_in_batches(gpu, params, seqs, budget, pool=None)
+    for i, part in enumerate(parts):
+        assert part.shape[0] == wl.lengths[i]
+        assert float((part.float() - ref[bounds[i]:bounds[i + 1]].float()).abs().max()) < 0.05

@@ -224,3 +224,23 @@ def test_shard_plan_balances_and_restores(pe):
     assert shard.local_pairs(np.array([10, 65, 66, 1000])).tolist() == [100, 4225, 4354, 124840]
     with pytest.raises(ValueError):
         shard.plan_shards([], 2)
+
+
+def test_token_budget_batches_follow_the_greedy_rule(pe):
+    """benchmarks/helpers/packed_training.py:175-202 of the reference: a new batch starts when the
+    next unit would exceed the budget; a batch always takes at least one unit."""
+    lengths = [5, 3, 9, 2, 2, 7, 1]
+    batches = pe.token_budget_batches(lengths, 10, sort_by_length=False)
+    assert batches == [[0, 1], [2], [3, 4], [5, 6]]
+    assert all(sum(lengths[i] for i in b) <= 10 for b in batches)
+    assert pe.token_budget_batches([30, 2], 10, sort_by_length=False) == [[0], [1]]   # oversize unit alone
+    longest_first = pe.token_budget_batches(lengths, 10)
+    assert sorted(i for b in longest_first for i in b) == list(range(7))
+    assert longest_first[0] == [2] and all(sum(lengths[i] for i in b) <= 10 for b in longest_first)
+    capped = pe.token_budget_batches([1] * 7, 100, max_sequences=3)
+    assert [len(b) for b in capped] == [3, 3, 1]
+    import pytest
+    with pytest.raises(ValueError):
+        pe.token_budget_batches([1, 0], 10)
+    with pytest.raises(ValueError):
+        pe.token_budget_batches([1], 0)
