@@ -13,6 +13,8 @@ tails (wasted work, as in packed_encoders/graph.py:244-248) but lie outside
 """
 from __future__ import annotations
 
+import warnings
+
 import os
 from collections import OrderedDict
 from dataclasses import dataclass
@@ -46,8 +48,10 @@ class GraphConfig:
     - `max_tokens`: totals above it are never captured.
     - `max_graphs`: LRU bound on live graphs.
     - `warmup`: eager runs on a side stream before capture.
-    - `seq_buckets`: accepted for source compatibility with the padded-API runner of the
-      reference; the packed runner has no sequence-length buckets to pre-capture.
+    - `seq_buckets` (with `max_batch`): graphs captured at `pack()` time instead of on first
+      sight, as packed_encoders/graph.py:410-427 does for the padded runner: one per listed
+      longest-sequence bound s, sized for `max_batch` sequences of s tokens. With
+      `token_buckets` (and `max_batch`) every listed budget is pre-captured as well.
     """
 
     pad_to: int = 64
@@ -184,6 +188,38 @@ class _PackedGraphRunner:
             _allow_graph=False,
         )
 
+    # -- pre-capture ---------------------------------------------------------
+    def precapture_keys(self) -> list[tuple[int, int, int]]:
+        """Cache keys to capture ahead of the first call, largest token capacity first (the
+        workspace then never has to grow, which would drop the graphs captured before)."""
+        cfg = self._config
+        if cfg.max_batch is None or not (cfg.seq_buckets or cfg.token_buckets):
+            return []
+        keys = set()
+        for s in cfg.seq_buckets or ():
+            key = self.bucket_for(cfg.max_batch * int(s), cfg.max_batch, int(s))
+            if key is not None:
+                keys.add(key)
+        if cfg.token_buckets:
+            longest = [int(s) for s in cfg.seq_buckets] if cfg.seq_buckets else [cfg.max_seq or (1 << 30)]
+            for budget in cfg.token_buckets:
+                for s in longest:
+                    key = self.bucket_for(int(budget), cfg.max_batch, min(s, int(budget)))
+                    if key is not None:
+                        keys.add(key)
+        return sorted(keys, reverse=True)[: cfg.max_graphs]
+
+    def precapture(self) -> int:
+        """Captures `precapture_keys()` now; returns how many graphs that made."""
+        binding = forward.get_binding(self._model, self._params)
+        self._generation = binding.generation
+        made = 0
+        for key in self.precapture_keys():
+            if key not in self._cache:
+                self._cache[key] = self._capture(*key)
+                made += 1
+        return made
+
     # -- capture ---------------------------------------------------------------
     def _ensure_workspace(self, binding, token_cap: int, seq_cap: int) -> Tensor:
         need = binding.workspace_bytes(token_cap, seq_cap)
@@ -234,7 +270,18 @@ class _PackedGraphRunner:
 def build_packed_runner(model: nn.Module, params: ModernBertParams, config: GraphConfig,
                         backend: str | None = None) -> _PackedGraphRunner:
     del backend
-    return _PackedGraphRunner(model, params, config)
+    runner = _PackedGraphRunner(model, params, config)
+    if config.seq_buckets or config.token_buckets:
+        if config.max_batch is None:
+            if config.seq_buckets:
+                warnings.warn(
+                    "GraphConfig.seq_buckets needs max_batch to know the sequence capacity to "
+                    "pre-capture at; skipping pre-capture (graphs are still captured on first sight).",
+                    stacklevel=2,
+                )
+        else:
+            runner.precapture()
+    return runner
 
 
 # ---------------------------------------------------------------------------

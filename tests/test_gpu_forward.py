@@ -354,3 +354,27 @@ def test_encode_in_token_budget_batches(pe, cuda_device, tiny_models):
     for i, part in enumerate(parts):
         assert part.shape[0] == wl.lengths[i]
         assert float((part.float() - ref[bounds[i]:bounds[i + 1]].float()).abs().max()) < 0.05
+
+
+def test_graphs_precaptured_at_pack_time(pe, cuda_device, tiny_models):
+    """`GraphConfig(seq_buckets=..., max_batch=...)` captures its graphs inside `pack()`, as
+    packed_encoders/graph.py:410-427 does: the first real calls are replays, not captures."""
+    _, _, gpu, vocab = tiny_models
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    cfg = pe.GraphConfig(pad_to=256, max_batch=16, max_seq=48, seq_buckets=(16, 48))
+    pe.pack(gpu, validate=False, cuda_graph=cfg)
+    try:
+        runner = pe.get_state(gpu).packed_graph_runner
+        assert runner.captures == 2 and sorted(runner._cache) == [(256, 16, 16), (768, 16, 64)]
+        gen = torch.Generator().manual_seed(9)
+        for lengths in ([16] * 16, [40] * 16, [48] * 9 + [33, 47, 35]):   # 256, 640 and 547 tokens
+            seqs = [torch.randint(5, vocab, (l,), generator=gen) for l in lengths]
+            batch = pe.pack_sequences(seqs, device=cuda_device)
+            with torch.no_grad():
+                graphed = pe.packed_forward(gpu, params, *batch.forward_args())
+                with pe.no_cuda_graph(gpu):
+                    eager = pe.packed_forward(gpu, params, *batch.forward_args())
+            assert torch.equal(graphed, eager)
+        assert runner.captures == 2 and runner.replays == 3      # nothing captured lazily
+    finally:
+        pe.unpack(gpu)

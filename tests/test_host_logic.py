@@ -138,6 +138,14 @@ def test_graph_bucket_policy(pe):
     assert runner.bucket_for(1000, 5, 100) == (1024, 8, 128)
     assert runner.bucket_for(1025, 9, 96) == (4096, 16, 64)
     assert runner.bucket_for(16385, 9, 100) is None
+    # graphs captured at pack() time: packed_encoders/graph.py:410-427 pre-captures the listed
+    # sequence buckets at max_batch rows; here one key per bucket, largest capacity first
+    runner._config = pe.GraphConfig(pad_to=256, max_batch=64, max_seq=64, seq_buckets=(16, 32, 64))
+    assert runner.precapture_keys() == [(4096, 64, 64), (2048, 64, 32), (1024, 64, 16)]
+    runner._config = pe.GraphConfig(max_batch=8, token_buckets=(1024, 4096), max_seq=48)
+    assert runner.precapture_keys() == [(4096, 8, 64), (1024, 8, 64)]
+    runner._config = pe.GraphConfig(seq_buckets=(16,))          # no max_batch: nothing to size them by
+    assert runner.precapture_keys() == []
 
 
 def test_graph_runner_lru_with_fakes(pe, monkeypatch):
