@@ -129,3 +129,31 @@ def gather_embeddings(local_out: Tensor, plan: ShardPlan, group=None) -> Tensor:
             dist.all_gather(parts, padded, group=group)
     index = torch.from_numpy(plan.restore_index).to(local_out.device)
     return gathered.index_select(0, index)
+
+
+def gather_pooled(local_pooled: Tensor, plan: ShardPlan, group=None) -> Tensor:
+    """All ranks receive the `[N, H]` per-sequence embeddings in the original sequence order.
+
+    The gather that follows a pooling head (`ops.pool_packed`): each rank contributes one row
+    per sequence of its group, `[N_r, H]`, padded to the largest group, so a multi-GPU
+    encode moves N * H values over NVLink instead of T * H."""
+    import torch.distributed as dist
+
+    world = plan.world_size
+    width = local_pooled.shape[-1]
+    max_rows = max(1, max(len(g) for g in plan.groups))
+    padded = local_pooled.new_zeros(max_rows, width)
+    padded[: local_pooled.shape[0]] = local_pooled
+    if world == 1:
+        gathered = padded
+    else:
+        gathered = local_pooled.new_empty(world * max_rows, width)
+        if dist.get_backend(group) == "nccl":
+            dist.all_gather_into_tensor(gathered, padded, group=group)
+        else:
+            parts = list(gathered.view(world, max_rows, width).unbind(0))
+            dist.all_gather(parts, padded, group=group)
+    index = np.empty(len(plan.lengths), dtype=np.int64)
+    for r, g in enumerate(plan.groups):
+        index[np.asarray(g, dtype=np.int64)] = r * max_rows + np.arange(len(g))
+    return gathered.index_select(0, torch.from_numpy(index).to(local_pooled.device))

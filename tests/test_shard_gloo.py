@@ -45,6 +45,16 @@ def _worker(rank: int, world: int, port: int, lengths, result_dir: str):
             for i in g:
                 owners[starts[i]:starts[i + 1]] = r
         assert np.array_equal(full[:, 2].numpy().astype(np.int64), owners)
+        # the pooled gather: one row per sequence, back in the callers' order
+        first_ids = torch.stack([m[0].float() for m in mine]) if mine else torch.zeros(0)
+        pooled = torch.stack([first_ids, torch.full_like(first_ids, float(rank))], dim=1)
+        all_pooled = shard.gather_pooled(pooled, plan)
+        assert all_pooled.shape == (len(lengths), 2)
+        assert torch.equal(all_pooled[:, 0], torch.tensor(starts[:-1], dtype=torch.float32))
+        seq_owner = np.empty(len(lengths), dtype=np.int64)
+        for r, g in enumerate(plan.groups):
+            seq_owner[np.asarray(g, dtype=np.int64)] = r
+        assert np.array_equal(all_pooled[:, 1].numpy().astype(np.int64), seq_owner)
         with open(os.path.join(result_dir, f"ok{rank}"), "w") as f:
             f.write("ok")
     finally:
@@ -65,3 +75,6 @@ def test_single_rank_is_identity():
     seqs = list(torch.split(torch.arange(12), [4, 2, 6]))
     local = torch.cat(shard.local_batch(plan, 0, seqs)).float().unsqueeze(1)
     assert torch.equal(shard.gather_embeddings(local, plan)[:, 0], torch.arange(12).float())
+    pooled = torch.tensor([[0.0], [4.0], [6.0]])                       # one row per sequence, callers' order
+    local_rows = pooled[torch.from_numpy(np.asarray(plan.groups[0]))]   # as rank 0 produces them
+    assert torch.equal(shard.gather_pooled(local_rows, plan), pooled)
