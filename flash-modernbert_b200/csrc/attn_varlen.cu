@@ -133,16 +133,21 @@ __device__ __forceinline__ void load_tile_async(uint32_t smem_tile, const __nv_b
 }
 
 template <int NWARPS>
-__global__ void __launch_bounds__(NWARPS * 32)
+__global__ void __launch_bounds__(NWARPS * 32, 16 / NWARPS)  // 16 warps per SM: 128 registers
 attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __restrict__ tile_info,
                        const int32_t* __restrict__ total_tiles_ptr, int nh, int half_window,
                        __nv_bfloat16* __restrict__ out) {
   constexpr int BM = NWARPS * 16;
   constexpr int THREADS = NWARPS * 32;
-  __shared__ __align__(128) uint8_t smem[BM * 128 + 4 * ATT_BN * 128];
-  const uint32_t sQ = smem_u32(smem);
-  const uint32_t sK = sQ + BM * 128;
-  const uint32_t sV = sK + 2 * ATT_BN * 128;
+  // One CTA serves a query tile for several heads (blockIdx.y, blockIdx.y + gridDim.y, ...), with
+  // two shared-memory stages of (Q, one K tile, one V tile): the loads of the next head are in
+  // flight while this head is computed.  The kernel is latency bound - one short global round
+  // trip and a few hundred MMAs per (tile, head) - so what counts is never waiting for that
+  // round trip with nothing else to do.  The sequences it serves (at most 64 tokens) have a
+  // single key tile.
+  constexpr int STAGE_BYTES_ = BM * 128 + 2 * ATT_BN * 128;
+  __shared__ __align__(128) uint8_t smem[2 * STAGE_BYTES_];
+  const uint32_t smem0 = smem_u32(smem);
 
   const int tile = blockIdx.x;
   if (tile >= *total_tiles_ptr) return;
@@ -150,12 +155,8 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
   const int seq_begin = info.x;
   const int len = info.y;
   const int q0 = info.z;
-  const int head = blockIdx.y;
   const int H = nh * ATT_D;
   const int64_t stride = 3 * int64_t(H);
-  const __nv_bfloat16* qg = qkv + int64_t(seq_begin) * stride + head * ATT_D;
-  const __nv_bfloat16* kg = qg + H;
-  const __nv_bfloat16* vg = qg + 2 * H;
 
   int kv_lo = 0, kv_hi = len;
   if (half_window >= 0) {
@@ -165,11 +166,32 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
   const int n_kv = (kv_hi - kv_lo + ATT_BN - 1) / ATT_BN;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float scale_log2 = 0.125f * 1.4426950408889634f;
+  const int row_in_warp = lane >> 2;           // rows r and r + 8 of this warp's 16
+  const int qrow0 = q0 + warp * 16 + row_in_warp;  // position in sequence of row r
+  // Warps whose 16 rows lie past the end of the sequence only take part in the loads and barriers.
+  const bool active = q0 + warp * 16 < len;
 
-  load_tile_async<THREADS>(sQ, qg + int64_t(q0) * stride, stride, BM, len - q0);
-  load_tile_async<THREADS>(sK, kg + int64_t(kv_lo) * stride, stride, ATT_BN, kv_hi - kv_lo);
-  load_tile_async<THREADS>(sV, vg + int64_t(kv_lo) * stride, stride, ATT_BN, kv_hi - kv_lo);
-  cp_async_commit();
+  auto load_head = [&](int head, int stage) {
+    const uint32_t sQ_ = smem0 + stage * STAGE_BYTES_;
+    const __nv_bfloat16* qg_ = qkv + int64_t(seq_begin) * stride + head * ATT_D;
+    load_tile_async<THREADS>(sQ_, qg_ + int64_t(q0) * stride, stride, BM, len - q0);
+    load_tile_async<THREADS>(sQ_ + BM * 128, qg_ + H + int64_t(kv_lo) * stride, stride, ATT_BN, kv_hi - kv_lo);
+    load_tile_async<THREADS>(sQ_ + BM * 128 + ATT_BN * 128, qg_ + 2 * H + int64_t(kv_lo) * stride, stride,
+                             ATT_BN, kv_hi - kv_lo);
+    cp_async_commit();
+  };
+  load_head(blockIdx.y, 0);
+
+  int stage = 0;
+  for (int head = blockIdx.y; head < nh; head += gridDim.y, stage ^= 1) {
+  const uint32_t sQ = smem0 + stage * STAGE_BYTES_;
+  const uint32_t sK = sQ + BM * 128;
+  const uint32_t sV = sK + ATT_BN * 128;
+  const __nv_bfloat16* kg = qkv + int64_t(seq_begin) * stride + head * ATT_D + H;
+  const __nv_bfloat16* vg = kg + H;
+  const bool more = head + int(gridDim.y) < nh;
+  if (more) load_head(head + gridDim.y, stage ^ 1);  // the other stage was released by the barrier below
 
   float o_acc[8][4];
 #pragma unroll
@@ -179,22 +201,22 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};
   uint32_t qf[4][4];
-  const float scale_log2 = 0.125f * 1.4426950408889634f;
-  const int row_in_warp = lane >> 2;           // rows r and r + 8 of this warp's 16
-  const int qrow0 = q0 + warp * 16 + row_in_warp;  // position in sequence of row r
 
   for (int it = 0; it < n_kv; ++it) {
-    const int buf = it & 1;
-    cp_async_wait<0>();
-    __syncthreads();
-    if (it + 1 < n_kv) {
-      const int k0n = kv_lo + (it + 1) * ATT_BN;
-      load_tile_async<THREADS>(sK + (buf ^ 1) * ATT_BN * 128, kg + int64_t(k0n) * stride, stride,
-                               ATT_BN, kv_hi - k0n);
-      load_tile_async<THREADS>(sV + (buf ^ 1) * ATT_BN * 128, vg + int64_t(k0n) * stride, stride,
-                               ATT_BN, kv_hi - k0n);
+    if (it > 0) {  // a longer sequence (not selected by the dispatcher): reload this stage's K / V
+      __syncthreads();
+      const int k0n = kv_lo + it * ATT_BN;
+      load_tile_async<THREADS>(sK, kg + int64_t(k0n) * stride, stride, ATT_BN, kv_hi - k0n);
+      load_tile_async<THREADS>(sV, vg + int64_t(k0n) * stride, stride, ATT_BN, kv_hi - k0n);
       cp_async_commit();
+      cp_async_wait<0>();
+    } else if (more) {
+      cp_async_wait<1>();  // this head's tiles have landed; the next head's are still in flight
+    } else {
+      cp_async_wait<0>();
     }
+    __syncthreads();
+    if (!active) continue;
     if (it == 0) {
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
@@ -203,9 +225,13 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
         ldsm_x4(sQ + tile_off(r, c), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
       }
     }
-    const uint32_t kt = sK + buf * ATT_BN * 128;
-    const uint32_t vt = sV + buf * ATT_BN * 128;
+    const uint32_t kt = sK;
+    const uint32_t vt = sV;
     const int k0 = kv_lo + it * ATT_BN;
+    // 16-key blocks of this tile that hold any key of the sequence: the MMAs of the others are
+    // skipped (their scores are masked to -inf below, their P is 0).  mma.sync is the scarce
+    // resource of this kernel, and a 30-token query fills two of a tile's four blocks.
+    const int nkb = min(4, (kv_hi - k0 + 15) >> 4);
 
     // S = Q K^T for this warp's 16 rows x 64 keys
     float s[8][4];
@@ -217,6 +243,7 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
     for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
       for (int jp = 0; jp < 4; ++jp) {
+        if (jp >= nkb) break;
         const int mid = lane >> 3;
         const int r = (jp * 2 + (mid >> 1)) * 8 + (lane & 7);
         const int c = kk * 2 + (mid & 1);
@@ -277,6 +304,7 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
     // O += P V
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
+      if (kk >= nkb) break;
       uint32_t pa[4];
       pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
       pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -323,12 +351,14 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
       *reinterpret_cast<uint4*>(og + int64_t(q0 + r) * H + c * 8) = v;
     }
   }
+  __syncthreads();  // every warp is done with this stage before the head after next is loaded into it
+  }  // heads
 }
 
 int attn_pick_bm(int max_seqlen) {
   if (max_seqlen <= 16) return 16;
   if (max_seqlen <= 32) return 32;
-  if (max_seqlen <= 96) return 64;
+  if (max_seqlen <= 64) return 64;
   return 128;  // tensor-memory kernel (attn_tcgen05.cu)
 }
 
@@ -359,7 +389,9 @@ int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh
   PE_REQUIRE(max_tiles < (1ll << 31), "attention: too many tiles");
   if (bm == 128)
     return attn_run_tc(qkv, tile_info, total_ptr, max_tiles, T, nh, half_window, out, status, st);
-  dim3 grid((unsigned)max_tiles, (unsigned)nh);
+  // four heads per CTA (see the kernel): enough CTAs to fill the GPU, few enough that each hides
+  // its own load latency
+  dim3 grid((unsigned)max_tiles, (unsigned)((nh + 3) / 4));
   const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(qkv);
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   switch (bm) {

@@ -78,14 +78,14 @@ def query_tile_rows(max_seqlen: int) -> int:
         return 16
     if max_seqlen <= 32:
         return 32
-    if max_seqlen <= 96:
+    if max_seqlen <= 64:
         return 64
     return 128
 
 
 def _tile_class_seqlen(rows: int) -> int:
     """A max_seqlen that selects the `rows`-row query tile."""
-    return {16: 16, 32: 32, 64: 96}.get(rows, 1 << 30)
+    return {16: 16, 32: 32, 64: 64}.get(rows, 1 << 30)
 
 
 @dataclass

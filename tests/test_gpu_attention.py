@@ -50,7 +50,7 @@ def test_ragged_and_tile_edges(pe, cuda_device, half_window):
 @pytest.mark.parametrize("lengths", [[5], [16, 3, 16, 1], [32, 20, 7, 32], [48, 8, 30, 41, 19], [96, 65, 64, 80, 1]])
 @pytest.mark.parametrize("half_window", [None, 64])
 def test_short_query_tiles(pe, cuda_device, lengths, half_window):
-    """max_seqlen <= 16 / <= 32 / <= 96 select the 16-, 32- and 64-row register-tiled kernels;
+    """max_seqlen <= 16 / <= 32 / <= 64 select the 16-, 32- and 64-row register-tiled kernels;
     longer batches take the 128-row tensor-memory kernel (the other tests)."""
     qkv, cu = _qkv(lengths, 4, cuda_device, seed=1)
     out = _run(qkv, cu, 4, half_window, cuda_device)

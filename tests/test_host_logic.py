@@ -136,7 +136,8 @@ def test_graph_bucket_policy(pe):
     assert runner.bucket_for(50001, 3, 16) is None       # over max_tokens
     runner._config = pe.GraphConfig(token_buckets=(1024, 4096, 16384))
     assert runner.bucket_for(1000, 5, 100) == (1024, 8, 128)
-    assert runner.bucket_for(1025, 9, 96) == (4096, 16, 64)
+    assert runner.bucket_for(1025, 9, 64) == (4096, 16, 64)
+    assert runner.bucket_for(1025, 9, 65) == (4096, 16, 128)
     assert runner.bucket_for(16385, 9, 100) is None
     # graphs captured at pack() time: packed_encoders/graph.py:410-427 pre-captures the listed
     # sequence buckets at max_batch rows; here one key per bucket, largest capacity first
