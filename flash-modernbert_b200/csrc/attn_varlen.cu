@@ -7,11 +7,13 @@
 // and sequence capacities and can be captured in a CUDA graph while the real
 // boundaries stay in device memory.
 //
-// This file holds the register-tiled kernel: NWARPS warps per CTA, 16 query rows
-// per warp, 64-key tiles double-buffered with cp.async, online softmax in fp32 in
-// the exp2 domain, P rounded to bf16 for the P*V product.  NWARPS is chosen from
-// max_seqlen, which gives the short-query tiles that ~30-token sequences want
-// (one 32-row CTA covers a whole sequence) and 64-row tiles otherwise.
+// This file holds the register-tiled kernel for batches whose longest sequence is at most 64
+// tokens (one key tile): NWARPS warps per CTA, 16 query rows per warp, mma.sync m16n8k16, online
+// softmax in fp32 in the exp2 domain, P rounded to bf16 for the P*V product.  NWARPS is chosen
+// from max_seqlen, which gives the short-query tiles that ~30-token sequences want (one 32-row
+// CTA covers a whole sequence).  A CTA serves its query tile for four heads; the next head's
+// Q / K / V tiles arrive by cp.async while the current one is computed.  Longer batches take the
+// tensor-memory kernels (attn_global_tcgen05.cu, attn_local_tcgen05.cu).
 #include <algorithm>
 #include <mutex>
 
