@@ -13,10 +13,11 @@ sm_100a CUDA behind a C ABI, include/pe_b200.h); there is no fallback path.
 """
 from __future__ import annotations
 
-from .collate import PackedBatch, encode_in_batches, pack_sequences, token_budget_batches
+from .collate import (PackedBatch, ServingWindow, encode_in_batches, encode_window, mixed_windows,
+                      pack_sequences, plan_windows, token_budget_batches)
 from .config import ModernBertParams
 from .errors import PackedEncodersError, UnsupportedTargetError, ValidationError
-from .forward import fused_forward, packed_forward
+from .forward import fused_forward, packed_forward, packed_forward_pooled
 from .graph import GraphConfig, no_cuda_graph, set_cuda_graph
 from .locate import find_encoder
 from .pack import pack, unpack
@@ -32,6 +33,7 @@ __all__ = [
     "set_cuda_graph",
     "no_cuda_graph",
     "packed_forward",
+    "packed_forward_pooled",
     "fused_forward",
     "ModernBertParams",
     "PatchState",
@@ -41,6 +43,10 @@ __all__ = [
     "PackedBatch",
     "token_budget_batches",
     "encode_in_batches",
+    "ServingWindow",
+    "mixed_windows",
+    "plan_windows",
+    "encode_window",
     "PackedEncodersError",
     "UnsupportedTargetError",
     "ValidationError",

@@ -30,10 +30,7 @@ _ERR_NAMES = {
 }
 OPT_FUSED_GEGLU = 1
 OPT_FUSED_ROPE = 2
-OPT_LOCAL_ATTN_SINGLE_PASS = 3
 OPT_FUSED_RESIDUAL = 4
-OPT_ATTN_TWO_CTA = 5
-OPT_LOCAL_ATTN_TWO_CTA = 6
 
 
 class NativeLibraryError(PackedEncodersError):
@@ -84,6 +81,9 @@ PROTOTYPES = {
                                c_void_p, c_void_p, POINTER(c_int32), c_void_p]),
     "pe_gather_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "pe_repad_scatter": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "pe_gather_rows_counted": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "pe_repad_scatter_counted": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
+                                         c_void_p]),
     "pe_rope_table": (c_int, [c_float, c_int, c_void_p, c_void_p]),
     "pe_embed_ln": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int64, c_int, c_int, c_void_p,
                             c_void_p, c_void_p]),
@@ -112,6 +112,9 @@ PROTOTYPES = {
     "pe_forward_workspace_bytes": (c_size_t, [POINTER(PeModel), c_int64, c_int]),
     "pe_forward_packed": (c_int, [POINTER(PeModel), c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                   c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
+    "pe_forward_packed_pooled": (c_int, [POINTER(PeModel), c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                         c_int, c_void_p, c_size_t, c_int, c_int, c_void_p, c_void_p,
+                                         c_void_p, c_void_p]),
     "pe_read_status": (c_int, [c_void_p, POINTER(c_int32), c_void_p]),
 }
 

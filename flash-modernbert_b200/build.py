@@ -21,7 +21,7 @@ INCLUDE = HERE.parent / "include"
 OBJ_DIR = HERE / "build"
 LIB_PATH = HERE / "libpe_b200.so"
 
-SOURCES = ["pe_host.cu", "tails.cu", "gemm_tcgen05.cu", "attn_varlen.cu", "attn_tcgen05.cu", "attn_global_tcgen05.cu", "attn_local_tcgen05.cu", "pool.cu", "forward.cu"]
+SOURCES = ["pe_host.cu", "tails.cu", "gemm_tcgen05.cu", "attn_varlen.cu", "attn_global_tcgen05.cu", "attn_local_tcgen05.cu", "pool.cu", "forward.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -91,8 +91,7 @@ def encode_in_batches(model, params, sequences, token_budget: int, *, pool: str 
     order of `sequences`: `[N, H]` sentence embeddings for `pool="mean"` / `"cls"`, or a list
     of per-sequence `[L_i, H]` hidden states for `pool=None`. Workspace and CUDA-graph buckets
     are bounded by the budget, whatever the corpus size."""
-    from . import ops
-    from .forward import packed_forward
+    from .forward import packed_forward, packed_forward_pooled
 
     seqs = list(sequences)
     if not seqs:
@@ -104,14 +103,88 @@ def encode_in_batches(model, params, sequences, token_budget: int, *, pool: str 
     for indices in token_budget_batches(lengths, token_budget, sort_by_length=sort_by_length,
                                         max_sequences=max_sequences):
         batch = pack_sequences([seqs[i] for i in indices], device=device)
-        hidden = packed_forward(model, params, *batch.forward_args())
         if pool is None:
+            hidden = packed_forward(model, params, *batch.forward_args())
             bounds = batch.cu_seqlens.tolist()
             for slot, i in enumerate(indices):
                 hidden_list[i] = hidden[bounds[slot]:bounds[slot + 1]]
             continue
-        emb = ops.pool_packed(hidden, batch.cu_seqlens, pool, normalize)
+        # pooling runs inside the final LayerNorm: the [T, H] hidden state is never materialised
+        emb = packed_forward_pooled(model, params, *batch.forward_args(), pool=pool, normalize=normalize)
         if pooled is None:
             pooled = torch.empty(len(seqs), emb.shape[-1], dtype=emb.dtype, device=emb.device)
         pooled[torch.tensor(indices, device=emb.device)] = emb
     return hidden_list if pool is None else pooled
+
+
+# ---------------------------------------------------------------------------
+# Serving windows that mix queries and documents
+# ---------------------------------------------------------------------------
+
+
+@dataclass
+class ServingWindow:
+    """One window of requests encoded as ONE packed batch, whatever mix of short queries and
+    long documents it holds (benchmarks/showcases/mixed_serving.py:151-193, `unified_packed`).
+
+    `requests[n]` is the caller's id of the n-th sequence of `batch`; `kinds[n]` its kind."""
+
+    requests: list[int]
+    kinds: list[str]
+    batch: PackedBatch
+
+
+def mixed_windows(kinds, lengths, *, requests_per_window: int, query_fraction: float, windows: int,
+                  seed: int = 0) -> list[list[int]]:
+    """Request indices of `windows` serving windows, each holding
+    `round(requests_per_window * query_fraction)` queries and the rest documents, drawn
+    without replacement inside a window and shuffled into arrival order: the sampling of
+    benchmarks/showcases/mixed_serving.py:151-172. `kinds[i]` is "query" or "document"."""
+    import random
+
+    n_query = round(requests_per_window * query_fraction)
+    n_document = requests_per_window - n_query
+    if not n_query or not n_document:
+        raise ValueError("each window must contain both query and document requests")
+    by_kind = {k: [i for i, kind in enumerate(kinds) if kind == k] for k in ("query", "document")}
+    if len(by_kind["query"]) < n_query or len(by_kind["document"]) < n_document:
+        raise ValueError("not enough requests of each kind to fill a window")
+    del lengths  # the draw does not look at lengths; kept in the signature for bucket-aware callers
+    rng = random.Random(int(seed))
+    out = []
+    for _ in range(int(windows)):
+        chosen = rng.sample(by_kind["query"], n_query) + rng.sample(by_kind["document"], n_document)
+        rng.shuffle(chosen)
+        out.append(chosen)
+    return out
+
+
+def plan_windows(lengths, *, token_buckets, max_sequences: int | None = None) -> list[list[int]]:
+    """Arrival-order windows sized for CUDA-graph token buckets: requests are taken in order and a
+    window is closed when the next request would push it past the LARGEST bucket (or past
+    `max_sequences`); each window then replays the smallest captured bucket that holds it.
+    Unlike `token_budget_batches` nothing is reordered, so a window holds whatever mix of queries
+    and documents arrived together; the attention schedule sends each sequence to the kernel that
+    suits its length, so mixing costs nothing."""
+    budgets = sorted(int(b) for b in token_buckets)
+    if not budgets or budgets[0] <= 0:
+        raise ValueError("plan_windows needs positive token_buckets")
+    return token_budget_batches(lengths, budgets[-1], sort_by_length=False, max_sequences=max_sequences)
+
+
+def encode_window(model, params, sequences, requests=None, kinds=None, *, pool: str | None = None,
+                  normalize: bool = True, device=None):
+    """Encodes one mixed window as a single packed batch in arrival order. Returns
+    `(ServingWindow, result)` where result is the packed `[T, H]` hidden state (`pool=None`; slice it
+    with `window.batch.cu_seqlens`) or `[N, H]` pooled embeddings, row n belonging to
+    `window.requests[n]`."""
+    from .forward import packed_forward, packed_forward_pooled
+
+    seqs = list(sequences)
+    device = device if device is not None else next(model.parameters()).device
+    batch = pack_sequences(seqs, device=device)
+    window = ServingWindow(list(requests) if requests is not None else list(range(len(seqs))),
+                           list(kinds) if kinds is not None else ["?"] * len(seqs), batch)
+    if pool is None:
+        return window, packed_forward(model, params, *batch.forward_args())
+    return window, packed_forward_pooled(model, params, *batch.forward_args(), pool=pool, normalize=normalize)

@@ -425,16 +425,10 @@ attn_local_tc2_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
 int attn_run_local_tc2(const void* qkv, const int4* tile_info, const int32_t* total_tiles,
                        int64_t max_tiles, int64_t T, int nh, void* out, int32_t* status,
                        cudaStream_t st) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    PE_CUDA(cudaFuncSetAttribute(attn_local_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 LW_SMEM));
-    PE_CUDA(cudaFuncSetAttribute(attn_local_tc2_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                 cudaSharedmemCarveoutMaxShared));
-    attr_set = true;
-  }
+  int rc = set_max_dynamic_smem(reinterpret_cast<const void*>(attn_local_tc2_kernel), LW_SMEM, true);
+  if (rc != PE_OK) return rc;
   CUtensorMap tm;
-  int rc = make_tmap_bf16_2d(&tm, qkv, (uint64_t)T, (uint64_t)(3 * nh * 64), (uint64_t)(3 * nh * 64),
+  rc = make_tmap_bf16_2d(&tm, qkv, (uint64_t)T, (uint64_t)(3 * nh * 64), (uint64_t)(3 * nh * 64),
                              128);
   if (rc != PE_OK) return rc;
   const int64_t max_items = max_tiles * nh;

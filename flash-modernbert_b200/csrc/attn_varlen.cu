@@ -25,58 +25,75 @@ namespace pe {
 constexpr int ATT_BN = 64;  // keys per tile
 constexpr int ATT_D = 64;
 
-// tile_start[n] = number of query tiles of sequences 0..n-1; tile_start[n_seqs] = total.
-// tile_info[t] = {first token of the sequence, sequence length, first query row of the tile, sequence}.
-__global__ void attn_schedule_kernel(const int32_t* __restrict__ cu_seqlens, int n_seqs, int bm,
-                                     int32_t* __restrict__ tile_start, int4* __restrict__ tile_info) {
-  __shared__ int warp_sums[32];
-  __shared__ int carry_s;
+// One pass over cu_seqlens builds the query-tile tables every attention launch of a forward reads.
+// Sequences longer than `short_max` go to the main table in tiles of `bm` rows:
+//   tile_start[n] = number of such tiles of sequences 0..n-1, tile_start[n_seqs] = their total,
+//   tile_info[t]  = {first token of the sequence, sequence length, first query row of the tile, sequence}.
+// Sequences of at most `short_max` tokens (short_max = 0: none) get one entry each in a second
+// table, short_info, counted by short_start[] in the same way: in a window that mixes ~30-token
+// queries with documents they are served by the register-tiled kernel below instead of paying for a
+// 128-row tensor-memory tile per query and head.
+// The boundaries are never trusted: a begin or end outside [0, T] or an end before its begin is
+// clamped into range and reported as ST_BAD_CU_SEQLENS, and no more than `cap_long` main tiles are
+// written, so that neither this kernel nor the ones that follow the descriptors can leave the
+// caller's buffers.
+__global__ void attn_schedule_kernel(const int32_t* __restrict__ cu_seqlens, int n_seqs, int T, int bm,
+                                     int short_max, int cap_long, int32_t* __restrict__ tile_start,
+                                     int32_t* __restrict__ short_start, int4* __restrict__ tile_info,
+                                     int4* __restrict__ short_info, int* status) {
+  __shared__ unsigned long long warp_sums[32];
+  __shared__ unsigned long long carry_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) {
-    carry_s = 0;
+    carry_s = 0ull;
     tile_start[0] = 0;
+    short_start[0] = 0;
   }
   __syncthreads();
   for (int base = 0; base < n_seqs; base += blockDim.x) {
     const int i = base + threadIdx.x;
-    int v = 0;
+    int begin = 0, len = 0;
+    unsigned long long v = 0ull;  // low half: main-table tiles of this sequence; high half: short entries
     if (i < n_seqs) {
-      const int len = cu_seqlens[i + 1] - cu_seqlens[i];
-      v = len > 0 ? (len + bm - 1) / bm : 0;
+      const int b_raw = cu_seqlens[i], e_raw = cu_seqlens[i + 1];
+      begin = min(max(b_raw, 0), T);
+      const int end = min(max(e_raw, begin), T);
+      if (b_raw != begin || e_raw != end) set_status(status, ST_BAD_CU_SEQLENS);
+      len = end - begin;
+      if (len > 0) v = (len <= short_max) ? (1ull << 32) : (unsigned long long)((len + bm - 1) / bm);
     }
-    int incl = v;
+    unsigned long long incl = v;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      const unsigned long long n = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += n;
     }
     if (lane == 31) warp_sums[warp] = incl;
     __syncthreads();
     if (warp == 0) {
-      int w = (lane < (blockDim.x >> 5)) ? warp_sums[lane] : 0;
+      unsigned long long w = (lane < (blockDim.x >> 5)) ? warp_sums[lane] : 0ull;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        const int n = __shfl_up_sync(0xffffffffu, w, o);
+        const unsigned long long n = __shfl_up_sync(0xffffffffu, w, o);
         if (lane >= o) w += n;
       }
       warp_sums[lane] = w;
     }
     __syncthreads();
-    const int warp_off = (warp == 0) ? 0 : warp_sums[warp - 1];
-    const int carry = carry_s;
-    if (i < n_seqs) tile_start[i + 1] = carry + warp_off + incl;
+    const unsigned long long after = carry_s + (warp == 0 ? 0ull : warp_sums[warp - 1]) + incl;
+    if (i < n_seqs) {
+      const unsigned long long before = after - v;
+      const int long_hi = (int)min((unsigned long long)cap_long, after & 0xffffffffull);
+      const int long_lo = (int)min((unsigned long long)cap_long, before & 0xffffffffull);
+      if ((after & 0xffffffffull) > (unsigned long long)cap_long) set_status(status, ST_BAD_CU_SEQLENS);
+      tile_start[i + 1] = long_hi;
+      short_start[i + 1] = (int)(after >> 32);
+      for (int t = long_lo; t < long_hi; ++t) tile_info[t] = make_int4(begin, len, (t - long_lo) * bm, i);
+      if ((v >> 32) != 0ull) short_info[(int)(before >> 32)] = make_int4(begin, len, 0, i);
+    }
     __syncthreads();
-    if (threadIdx.x == 0) carry_s = carry + warp_sums[(blockDim.x >> 5) - 1];
+    if (threadIdx.x == 0) carry_s += warp_sums[(blockDim.x >> 5) - 1];
     __syncthreads();
-  }
-  __threadfence_block();
-  __syncthreads();
-  for (int i = threadIdx.x; i < n_seqs; i += blockDim.x) {
-    const int begin = cu_seqlens[i];
-    const int len = cu_seqlens[i + 1] - begin;
-    const int first = tile_start[i];
-    const int n = tile_start[i + 1] - first;
-    for (int t = 0; t < n; ++t) tile_info[first + t] = make_int4(begin, len, t * bm, i);
   }
 }
 
@@ -361,50 +378,65 @@ int attn_pick_bm(int max_seqlen) {
   if (max_seqlen <= 16) return 16;
   if (max_seqlen <= 32) return 32;
   if (max_seqlen <= 64) return 64;
-  return 128;  // tensor-memory kernel (attn_tcgen05.cu)
+  return 128;  // tensor-memory kernels, with the sequences of at most 64 tokens on the register kernel
 }
 
-// Scratch layout: tile_start int32[n_seqs + 1], padded to 16 bytes, then tile_info int4[max tiles].
-static size_t info_offset(int n_seqs) { return (size_t(n_seqs + 2) * sizeof(int32_t) + 15) & ~size_t(15); }
-size_t attn_info_offset(int n_seqs) { return info_offset(n_seqs); }
+// Sequences of at most this many tokens form the short class of a batch scheduled with 128-row tiles.
+constexpr int ATT_SHORT_MAX = 64;
 
-size_t attn_scratch_bytes(int64_t T, int n_seqs) {
-  return info_offset(n_seqs) + size_t(T / 16 + n_seqs + 1) * sizeof(int4);
+// Scratch layout: tile_start int32[n_seqs + 1], short_start int32[n_seqs + 1], padded to 16 bytes,
+// then tile_info int4[T / bm + n_seqs] and short_info int4[n_seqs].  The size is taken for the
+// smallest tile height (16), which bounds every other.
+constexpr size_t info_offset_c(int n_seqs) { return (size_t(2 * n_seqs + 2) * sizeof(int32_t) + 15) & ~size_t(15); }
+constexpr size_t scratch_bytes_c(int64_t T, int n_seqs) {
+  return info_offset_c(n_seqs) + size_t(T / 16 + 2 * int64_t(n_seqs) + 2) * sizeof(int4);
+}
+size_t attn_info_offset(int n_seqs) { return info_offset_c(n_seqs); }
+size_t attn_scratch_bytes(int64_t T, int n_seqs) { return scratch_bytes_c(T, n_seqs); }
+
+struct TileTables {
+  int32_t* tile_start;
+  int32_t* short_start;
+  int4* tile_info;
+  int4* short_info;
+  int cap_long;
+};
+static TileTables tile_tables(void* scratch, int n_seqs, int64_t T, int bm) {
+  TileTables t;
+  t.tile_start = static_cast<int32_t*>(scratch);
+  t.short_start = t.tile_start + n_seqs + 1;
+  t.tile_info = reinterpret_cast<int4*>(static_cast<uint8_t*>(scratch) + info_offset_c(n_seqs));
+  t.cap_long = int(T / bm + n_seqs);
+  t.short_info = t.tile_info + t.cap_long;
+  return t;
 }
 
-int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int bm, void* scratch, cudaStream_t st) {
-  int32_t* tile_start = static_cast<int32_t*>(scratch);
-  int4* tile_info = reinterpret_cast<int4*>(static_cast<uint8_t*>(scratch) + info_offset(n_seqs));
-  attn_schedule_kernel<<<1, 1024, 0, st>>>(cu_seqlens, n_seqs, bm, tile_start, tile_info);
+int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int64_t T, int bm, bool split_short,
+                  void* scratch, int32_t* status, cudaStream_t st) {
+  PE_REQUIRE(T >= 0 && T < (1ll << 31) - 256 && n_seqs > 0 && T / bm + n_seqs < (1ll << 31),
+             "attention schedule: %lld tokens / %d sequences out of range", (long long)T, n_seqs);
+  const TileTables t = tile_tables(scratch, n_seqs, T, bm);
+  attn_schedule_kernel<<<1, 1024, 0, st>>>(cu_seqlens, n_seqs, (int)T, bm,
+                                           split_short ? ATT_SHORT_MAX : 0, t.cap_long, t.tile_start,
+                                           t.short_start, t.tile_info, t.short_info, status);
   PE_LAUNCH_CHECK("attn_schedule_kernel");
   return PE_OK;
 }
 
-int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh, int half_window,
-             int bm, void* out, int32_t* status, cudaStream_t st) {
-  const int32_t* tile_start = static_cast<const int32_t*>(scratch);
-  const int4* tile_info =
-      reinterpret_cast<const int4*>(static_cast<const uint8_t*>(scratch) + info_offset(n_seqs));
-  const int32_t* total_ptr = tile_start + n_seqs;
-  // Upper bound on the number of query tiles given only the capacities.
-  const int64_t max_tiles = T / bm + n_seqs;
-  PE_REQUIRE(max_tiles < (1ll << 31), "attention: too many tiles");
-  if (bm == 128)
-    return attn_run_tc(qkv, tile_info, total_ptr, max_tiles, T, nh, half_window, out, status, st);
+static int launch_short(const __nv_bfloat16* q, const int4* info, const int32_t* total, int64_t max_tiles,
+                        int bm, int nh, int half_window, __nv_bfloat16* o, cudaStream_t st) {
   // four heads per CTA (see the kernel): enough CTAs to fill the GPU, few enough that each hides
   // its own load latency
   dim3 grid((unsigned)max_tiles, (unsigned)((nh + 3) / 4));
-  const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(qkv);
-  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   switch (bm) {
     case 16:
-      attn_varlen_mma_kernel<1><<<grid, 32, 0, st>>>(q, tile_info, total_ptr, nh, half_window, o);
+      attn_varlen_mma_kernel<1><<<grid, 32, 0, st>>>(q, info, total, nh, half_window, o);
       break;
     case 32:
-      attn_varlen_mma_kernel<2><<<grid, 64, 0, st>>>(q, tile_info, total_ptr, nh, half_window, o);
+      attn_varlen_mma_kernel<2><<<grid, 64, 0, st>>>(q, info, total, nh, half_window, o);
       break;
     case 64:
-      attn_varlen_mma_kernel<4><<<grid, 128, 0, st>>>(q, tile_info, total_ptr, nh, half_window, o);
+      attn_varlen_mma_kernel<4><<<grid, 128, 0, st>>>(q, info, total, nh, half_window, o);
       break;
     default:
       set_last_error("attention: unsupported query tile %d", bm);
@@ -414,14 +446,30 @@ int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh
   return PE_OK;
 }
 
+int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh, int half_window,
+             int bm, void* out, int32_t* status, cudaStream_t st) {
+  const TileTables t = tile_tables(const_cast<void*>(scratch), n_seqs, T, bm);
+  const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(qkv);
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  if (bm != 128) return launch_short(q, t.tile_info, t.tile_start + n_seqs, t.cap_long, bm, nh, half_window, o, st);
+  // Long batch: the tensor-memory kernels take the sequences of more than 64 tokens (at most
+  // T / 128 + T / 65 tiles of them exist), the register kernel with 64-row tiles the rest.
+  const int64_t max_long = std::min<int64_t>(t.cap_long, T / 128 + T / (ATT_SHORT_MAX + 1) + 1);
+  int rc = (half_window == 64)
+               ? attn_run_local_tc2(qkv, t.tile_info, t.tile_start + n_seqs, max_long, T, nh, out, status, st)
+               : attn_run_global_tc(qkv, t.tile_info, t.tile_start + n_seqs, max_long, T, nh, half_window,
+                                    out, status, st);
+  if (rc != PE_OK) return rc;
+  const int64_t max_short = std::min<int64_t>(n_seqs, T);
+  return launch_short(q, t.short_info, t.short_start + n_seqs, max_short, 64, nh, half_window, o, st);
+}
+
 // ---- scratch that needs no allocation -------------------------------------------------
 // pe_attn_varlen_static keeps its tile table in this array instead of caller memory.  Every
 // GPU that loads the library carries the array from load until the process exits.
 constexpr int STATIC_MAX_SEQS = 4096;
 constexpr int64_t STATIC_MAX_TOKENS = 1 << 20;
-constexpr size_t STATIC_SCRATCH_BYTES =
-    ((size_t(STATIC_MAX_SEQS + 2) * sizeof(int32_t) + 15) & ~size_t(15)) +
-    size_t(STATIC_MAX_TOKENS / 16 + STATIC_MAX_SEQS + 1) * sizeof(int4);
+constexpr size_t STATIC_SCRATCH_BYTES = scratch_bytes_c(STATIC_MAX_TOKENS, STATIC_MAX_SEQS);
 static __device__ __align__(256) unsigned char g_attn_static_scratch[STATIC_SCRATCH_BYTES];
 
 // Device address of the array on the current device.  In host code the symbol's name is only
@@ -465,7 +513,7 @@ extern "C" int pe_attn_varlen_static(const void* qkv, const int32_t* cu_seqlens,
   const int bm = attn_pick_bm(max_seqlen);
   // The scheduling kernel rewrites every table entry this call reads, so nothing left by an
   // earlier call is used and nothing has to be cleared first.
-  rc = attn_schedule(cu_seqlens, n_seqs, bm, scratch, st);
+  rc = attn_schedule(cu_seqlens, n_seqs, T, bm, bm == 128, scratch, status, st);
   if (rc != PE_OK) return rc;
   return attn_run(qkv, scratch, n_seqs, T, nh, half_window, bm, out, status, st);
 }
@@ -492,7 +540,7 @@ extern "C" int pe_attn_varlen(const void* qkv, const int32_t* cu_seqlens, int n_
   if (T == 0) return PE_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int bm = attn_pick_bm(max_seqlen);
-  int rc = attn_schedule(cu_seqlens, n_seqs, bm, workspace, st);
+  int rc = attn_schedule(cu_seqlens, n_seqs, T, bm, bm == 128, workspace, status, st);
   if (rc != PE_OK) return rc;
   return attn_run(qkv, workspace, n_seqs, T, nh, half_window, bm, out, status, st);
 }

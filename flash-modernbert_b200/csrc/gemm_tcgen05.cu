@@ -423,14 +423,11 @@ static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_o
                        int w_rows, int gate_row0, RopeArgs rope, int32_t* status,
                        cudaStream_t stream) {
   constexpr bool GEGLU = MODE == GEMM_GEGLU;
-  static bool attr_set = false;  // one flag per instantiation
   auto kern = gemm_bf16_tn_kernel<MODE>;
-  if (!attr_set) {
-    PE_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
-    attr_set = true;
-  }
+  int rc = set_max_dynamic_smem(reinterpret_cast<const void*>(kern), GEMM_SMEM, false);
+  if (rc != PE_OK) return rc;
   CUtensorMap tmA, tmB;
-  int rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM);
+  rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM);
   if (rc != PE_OK) return rc;
   rc = make_tmap_bf16_2d(&tmB, W, (uint64_t)w_rows, (uint64_t)K, (uint64_t)K, 128);
   if (rc != PE_OK) return rc;

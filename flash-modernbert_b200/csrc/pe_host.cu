@@ -36,11 +36,34 @@ int sm_count() {
   return cached[dev];
 }
 
+int set_max_dynamic_smem(const void* func, int bytes, bool max_carveout) {
+  static std::mutex lock;
+  static const void* done_func[256];
+  static int done_dev[256];
+  static int n_done = 0;
+  int dev = 0;
+  PE_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> guard(lock);
+  for (int i = 0; i < n_done; ++i)
+    if (done_func[i] == func && done_dev[i] == dev) return PE_OK;
+  PE_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (max_carveout)
+    PE_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared));
+  if (n_done < 256) {  // beyond that the attribute is simply set again on every launch
+    done_func[n_done] = func;
+    done_dev[n_done] = dev;
+    ++n_done;
+  }
+  return PE_OK;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Bytes outside the tensor read as zero (FLOAT_OOB_FILL_NONE means "no NaN fill", i.e. zeros).
 // The driver entry point is resolved through the runtime so that the library
 // links against cudart only.
 static EncodeTiledFn encode_fn() {

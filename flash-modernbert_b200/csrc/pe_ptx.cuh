@@ -21,6 +21,7 @@ enum StatusCode : int {
   ST_ATTN_SMEM_MISALIGNED = 204,  // dynamic shared memory did not start on a 1024-byte boundary
   ST_BAD_TOKEN_ID = 301,
   ST_BAD_POSITION = 302,
+  ST_BAD_CU_SEQLENS = 303,  // a boundary outside [0, T] or running backwards (clamped, not followed)
 };
 
 __device__ __forceinline__ void set_status(int* status, int code) {

@@ -8,6 +8,7 @@
 
 #include "pe_host.h"
 #include "pe_ptx.cuh"
+#include "pe_vec.cuh"
 
 namespace pe {
 
@@ -121,15 +122,22 @@ static int unpad_launch(const void* mask, int B, int S, int32_t* seqlens, int32_
 // ------------------------------------------------------------------------------
 // row gather / re-pad scatter
 // ------------------------------------------------------------------------------
+// count_dev (may be NULL): the real number of packed rows, read on the device and clamped to T;
+// rows at or beyond it are written as zeros and their indices are not read.
 template <typename V>
 __global__ void gather_rows_kernel(const V* __restrict__ src, const int64_t* __restrict__ indices,
-                                   int64_t T, int vec_per_row, V* __restrict__ dst) {
+                                   int64_t T, const int32_t* __restrict__ count_dev, int vec_per_row,
+                                   V* __restrict__ dst) {
   const int64_t total = T * vec_per_row;
+  const int64_t real = count_dev ? min(max(int64_t(*count_dev), int64_t(0)), T) : T;
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total;
        i += int64_t(gridDim.x) * blockDim.x) {
     const int64_t t = i / vec_per_row;
     const int c = int(i - t * vec_per_row);
-    dst[i] = src[indices[t] * vec_per_row + c];
+    V v;
+    memset(&v, 0, sizeof(V));
+    if (t < real) v = src[indices[t] * vec_per_row + c];
+    dst[i] = v;
   }
 }
 
@@ -137,7 +145,9 @@ __global__ void gather_rows_kernel(const V* __restrict__ src, const int64_t* __r
 // found at t -> copy packed row t, else write zeros.  No memset pass.
 template <typename V>
 __global__ void repad_kernel(const V* __restrict__ packed, const int64_t* __restrict__ indices,
-                             int64_t T, int64_t rows_out, int vec_per_row, V* __restrict__ out) {
+                             int64_t T_cap, const int32_t* __restrict__ count_dev, int64_t rows_out,
+                             int vec_per_row, V* __restrict__ out) {
+  const int64_t T = count_dev ? min(max(int64_t(*count_dev), int64_t(0)), T_cap) : T_cap;
   const int lanes_per_row = min(vec_per_row, 32);
   const int rows_per_block = blockDim.x / lanes_per_row;
   const int sub = threadIdx.x / lanes_per_row;
@@ -172,31 +182,6 @@ static int pick_vec_bytes(const void* a, const void* b, int64_t row_bytes) {
 // LayerNorm family: one warp per row, row kept in registers between the
 // statistics pass and the normalise pass.  VPL = 16-byte vectors per lane.
 // ------------------------------------------------------------------------------
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(p[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-  uint4 o;
-  o.x = pack_bf16(f[0], f[1]);
-  o.y = pack_bf16(f[2], f[3]);
-  o.z = pack_bf16(f[4], f[5]);
-  o.w = pack_bf16(f[6], f[7]);
-  return o;
-}
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
 // MODE 0: y = LN(x).  MODE 1: x_new = bf16(x + res), y = LN(x_new).
 // MODE 2: x = tok_emb[ids[row]], y = LN(x).
 template <int VPL, int MODE>
@@ -471,52 +456,78 @@ extern "C" int pe_unpad_build(const void* mask, int mask_elt_bytes, int B, int S
   return PE_OK;
 }
 
-extern "C" int pe_gather_rows(const void* src, const int64_t* indices, int64_t T, int64_t row_bytes,
-                              void* dst, void* stream) {
-  PE_REQUIRE(src && indices && dst, "pe_gather_rows: null pointer");
-  PE_REQUIRE(T >= 0 && row_bytes > 0, "pe_gather_rows: bad sizes");
+static int gather_rows_launch(const void* src, const int64_t* indices, int64_t T,
+                              const int32_t* count_dev, int64_t row_bytes, void* dst, void* stream,
+                              const char* who) {
+  PE_REQUIRE(src && indices && dst, "%s: null pointer", who);
+  PE_REQUIRE(T >= 0 && row_bytes > 0, "%s: bad sizes", who);
   if (T == 0) return PE_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int vb = pick_vec_bytes(src, dst, row_bytes);
   const int64_t vpr = row_bytes / vb;
-  PE_REQUIRE(vpr < (1ll << 30), "pe_gather_rows: row too wide");
+  PE_REQUIRE(vpr < (1ll << 30), "%s: row too wide", who);
   const int64_t total = T * vpr;
   const int threads = 256;
-  const unsigned blocks = (unsigned)std::min<int64_t>((total + threads - 1) / threads, 148 * 32);
+  const unsigned blocks = (unsigned)std::min<int64_t>((total + threads - 1) / threads, (int64_t)sm_count() * 32);
   switch (vb) {
-    case 16: gather_rows_kernel<uint4><<<blocks, threads, 0, st>>>((const uint4*)src, indices, T, (int)vpr, (uint4*)dst); break;
-    case 8: gather_rows_kernel<uint2><<<blocks, threads, 0, st>>>((const uint2*)src, indices, T, (int)vpr, (uint2*)dst); break;
-    case 4: gather_rows_kernel<uint32_t><<<blocks, threads, 0, st>>>((const uint32_t*)src, indices, T, (int)vpr, (uint32_t*)dst); break;
-    case 2: gather_rows_kernel<uint16_t><<<blocks, threads, 0, st>>>((const uint16_t*)src, indices, T, (int)vpr, (uint16_t*)dst); break;
-    default: gather_rows_kernel<uint8_t><<<blocks, threads, 0, st>>>((const uint8_t*)src, indices, T, (int)vpr, (uint8_t*)dst); break;
+    case 16: gather_rows_kernel<uint4><<<blocks, threads, 0, st>>>((const uint4*)src, indices, T, count_dev, (int)vpr, (uint4*)dst); break;
+    case 8: gather_rows_kernel<uint2><<<blocks, threads, 0, st>>>((const uint2*)src, indices, T, count_dev, (int)vpr, (uint2*)dst); break;
+    case 4: gather_rows_kernel<uint32_t><<<blocks, threads, 0, st>>>((const uint32_t*)src, indices, T, count_dev, (int)vpr, (uint32_t*)dst); break;
+    case 2: gather_rows_kernel<uint16_t><<<blocks, threads, 0, st>>>((const uint16_t*)src, indices, T, count_dev, (int)vpr, (uint16_t*)dst); break;
+    default: gather_rows_kernel<uint8_t><<<blocks, threads, 0, st>>>((const uint8_t*)src, indices, T, count_dev, (int)vpr, (uint8_t*)dst); break;
   }
   PE_LAUNCH_CHECK("gather_rows_kernel");
   return PE_OK;
 }
 
-extern "C" int pe_repad_scatter(const void* packed, const int64_t* indices, int64_t T,
-                                int64_t rows_out, int64_t row_bytes, void* out, void* stream) {
-  PE_REQUIRE(out && (T == 0 || (packed && indices)), "pe_repad_scatter: null pointer");
-  PE_REQUIRE(T >= 0 && rows_out >= 0 && row_bytes > 0, "pe_repad_scatter: bad sizes");
+static int repad_launch(const void* packed, const int64_t* indices, int64_t T, const int32_t* count_dev,
+                        int64_t rows_out, int64_t row_bytes, void* out, void* stream, const char* who) {
+  PE_REQUIRE(out && (T == 0 || (packed && indices)), "%s: null pointer", who);
+  PE_REQUIRE(T >= 0 && rows_out >= 0 && row_bytes > 0, "%s: bad sizes", who);
   if (rows_out == 0) return PE_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int vb = pick_vec_bytes(packed ? packed : out, out, row_bytes);
   const int64_t vpr = row_bytes / vb;
-  PE_REQUIRE(vpr < (1ll << 30), "pe_repad_scatter: row too wide");
+  PE_REQUIRE(vpr < (1ll << 30), "%s: row too wide", who);
   const int threads = 256;
   const int lanes = (int)std::min<int64_t>(vpr, 32);
   const int rows_per_block = threads / lanes;
   const unsigned blocks =
-      (unsigned)std::min<int64_t>((rows_out + rows_per_block - 1) / rows_per_block, 148 * 64);
+      (unsigned)std::min<int64_t>((rows_out + rows_per_block - 1) / rows_per_block, (int64_t)sm_count() * 64);
   switch (vb) {
-    case 16: repad_kernel<uint4><<<blocks, threads, 0, st>>>((const uint4*)packed, indices, T, rows_out, (int)vpr, (uint4*)out); break;
-    case 8: repad_kernel<uint2><<<blocks, threads, 0, st>>>((const uint2*)packed, indices, T, rows_out, (int)vpr, (uint2*)out); break;
-    case 4: repad_kernel<uint32_t><<<blocks, threads, 0, st>>>((const uint32_t*)packed, indices, T, rows_out, (int)vpr, (uint32_t*)out); break;
-    case 2: repad_kernel<uint16_t><<<blocks, threads, 0, st>>>((const uint16_t*)packed, indices, T, rows_out, (int)vpr, (uint16_t*)out); break;
-    default: repad_kernel<uint8_t><<<blocks, threads, 0, st>>>((const uint8_t*)packed, indices, T, rows_out, (int)vpr, (uint8_t*)out); break;
+    case 16: repad_kernel<uint4><<<blocks, threads, 0, st>>>((const uint4*)packed, indices, T, count_dev, rows_out, (int)vpr, (uint4*)out); break;
+    case 8: repad_kernel<uint2><<<blocks, threads, 0, st>>>((const uint2*)packed, indices, T, count_dev, rows_out, (int)vpr, (uint2*)out); break;
+    case 4: repad_kernel<uint32_t><<<blocks, threads, 0, st>>>((const uint32_t*)packed, indices, T, count_dev, rows_out, (int)vpr, (uint32_t*)out); break;
+    case 2: repad_kernel<uint16_t><<<blocks, threads, 0, st>>>((const uint16_t*)packed, indices, T, count_dev, rows_out, (int)vpr, (uint16_t*)out); break;
+    default: repad_kernel<uint8_t><<<blocks, threads, 0, st>>>((const uint8_t*)packed, indices, T, count_dev, rows_out, (int)vpr, (uint8_t*)out); break;
   }
   PE_LAUNCH_CHECK("repad_kernel");
   return PE_OK;
+}
+
+extern "C" int pe_gather_rows(const void* src, const int64_t* indices, int64_t T, int64_t row_bytes,
+                              void* dst, void* stream) {
+  return gather_rows_launch(src, indices, T, nullptr, row_bytes, dst, stream, "pe_gather_rows");
+}
+
+extern "C" int pe_gather_rows_counted(const void* src, const int64_t* indices, const int32_t* count_dev,
+                                      int64_t capacity, int64_t row_bytes, void* dst, void* stream) {
+  PE_REQUIRE(count_dev != nullptr, "pe_gather_rows_counted: count_dev is NULL");
+  return gather_rows_launch(src, indices, capacity, count_dev, row_bytes, dst, stream,
+                            "pe_gather_rows_counted");
+}
+
+extern "C" int pe_repad_scatter(const void* packed, const int64_t* indices, int64_t T,
+                                int64_t rows_out, int64_t row_bytes, void* out, void* stream) {
+  return repad_launch(packed, indices, T, nullptr, rows_out, row_bytes, out, stream, "pe_repad_scatter");
+}
+
+extern "C" int pe_repad_scatter_counted(const void* packed, const int64_t* indices,
+                                        const int32_t* count_dev, int64_t capacity, int64_t rows_out,
+                                        int64_t row_bytes, void* out, void* stream) {
+  PE_REQUIRE(count_dev != nullptr, "pe_repad_scatter_counted: count_dev is NULL");
+  return repad_launch(packed, indices, capacity, count_dev, rows_out, row_bytes, out, stream,
+                      "pe_repad_scatter_counted");
 }
 
 extern "C" int pe_rope_table(float theta, int max_positions, void* table, void* stream) {
@@ -567,7 +578,7 @@ extern "C" int pe_geglu(const void* proj, int64_t T, int I, void* out, void* str
   if (T == 0) return PE_OK;
   const int64_t total = T * (I / 8);
   const int threads = 256;
-  const unsigned blocks = (unsigned)std::min<int64_t>((total + threads - 1) / threads, 148 * 64);
+  const unsigned blocks = (unsigned)std::min<int64_t>((total + threads - 1) / threads, (int64_t)sm_count() * 64);
   geglu_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(proj), T, I, static_cast<__nv_bfloat16*>(out));
   PE_LAUNCH_CHECK("geglu_kernel");

@@ -172,12 +172,24 @@ class ModelBinding:
             raise _lib.NativeLibraryError(
                 f"a CUDA kernel reported status {code} (1xx: GEMM pipeline wait gave up, "
                 "2xx: attention, 301: token id outside the vocabulary, 302: position outside "
-                "the RoPE table)"
+                "the RoPE table, 303: cu_seqlens entry outside [0, T] or decreasing)"
             )
+
+    def after_call(self) -> None:
+        """What every forward does once its kernels are enqueued: with PE_B200_CHECK_STATUS=1
+        wait and raise on this very call, else start the read-back of the status word that the
+        next call's `check()` inspects."""
+        if os.environ.get(_CHECK_ENV, "0") == "1":
+            self.check(sync=True)
+        else:
+            self._status_host.copy_(self._status, non_blocking=True)
 
     # -- the call ---------------------------------------------------------------
     def run(self, ids: Tensor, cu_seqlens: Tensor, position_ids: Tensor, max_seqlen: int,
-            out: Tensor, *, workspace: Tensor | None = None, refresh: bool = True) -> Tensor:
+            out: Tensor | None, *, workspace: Tensor | None = None, refresh: bool = True,
+            pooled: Tensor | None = None, pool_mode: int = 1, normalize: bool = True) -> Tensor | None:
+        """Enqueue one forward. `out` receives the `[T, H]` hidden state; with `pooled` (an
+        `[N, H]` tensor) the pooling head runs inside the final LayerNorm and `out` may be None."""
         total = ids.shape[0]
         n_seqs = cu_seqlens.shape[0] - 1
         if max_seqlen > self.max_positions:
@@ -187,11 +199,18 @@ class ModelBinding:
             self.refresh()
         ws = workspace if workspace is not None else self.workspace(total, n_seqs)
         with torch.cuda.device(self.device):
-            rc = self.lib.pe_forward_packed(
-                ctypes.byref(self._model_c), ids.data_ptr(), cu_seqlens.data_ptr(),
-                position_ids.data_ptr(), total, n_seqs, int(max_seqlen), ws.data_ptr(), ws.numel(),
-                out.data_ptr(), self._status.data_ptr(), _lib.current_stream_ptr())
-        _lib.check(rc, "pe_forward_packed")
+            if pooled is None:
+                rc = self.lib.pe_forward_packed(
+                    ctypes.byref(self._model_c), ids.data_ptr(), cu_seqlens.data_ptr(),
+                    position_ids.data_ptr(), total, n_seqs, int(max_seqlen), ws.data_ptr(), ws.numel(),
+                    out.data_ptr(), self._status.data_ptr(), _lib.current_stream_ptr())
+            else:
+                rc = self.lib.pe_forward_packed_pooled(
+                    ctypes.byref(self._model_c), ids.data_ptr(), cu_seqlens.data_ptr(),
+                    position_ids.data_ptr(), total, n_seqs, int(max_seqlen), ws.data_ptr(), ws.numel(),
+                    int(pool_mode), 1 if normalize else 0, _lib.ptr(out), pooled.data_ptr(),
+                    self._status.data_ptr(), _lib.current_stream_ptr())
+        _lib.check(rc, "pe_forward_packed" if pooled is None else "pe_forward_packed_pooled")
         return out
 
 
@@ -349,11 +368,57 @@ def packed_forward(
     if total == 0:
         return out
     binding.run(packed_ids, cu_seqlens, position_ids, int(max_seqlen), out)
-    if os.environ.get(_CHECK_ENV, "0") == "1":
-        binding.check(sync=True)
-    else:
-        binding._status_host.copy_(binding._status, non_blocking=True)
+    binding.after_call()
     return out
+
+
+def packed_forward_pooled(
+    model: nn.Module,
+    params: ModernBertParams,
+    packed_ids: Tensor,
+    cu_seqlens: Tensor,
+    max_seqlen: int,
+    position_ids: Tensor | None = None,
+    *,
+    pool: str = "mean",
+    normalize: bool = True,
+    return_hidden: bool = False,
+) -> Tensor | tuple[Tensor, Tensor]:
+    """`packed_forward` followed by the pooling every caller of the reference applies to its
+    result (benchmarks/showcases/inference.py:193-209: fp32 segment mean, `F.normalize`, cast
+    back), as one library call: the pooling runs inside the final LayerNorm, so the `[T, H]`
+    hidden state is not read back and, unless `return_hidden`, never written.
+
+    Returns `[N, H]` bf16 sentence embeddings (`pool="mean"` or `"cls"`), or
+    `(hidden [T, H], embeddings [N, H])` with `return_hidden=True`. Always eager (no graph replay).
+    """
+    if pool not in ("mean", "cls"):
+        raise ValueError(f"packed_forward_pooled: pool must be 'mean' or 'cls', got {pool!r}")
+    packed_ids = _require_cuda_tensor(packed_ids, "packed_ids", torch.int64)
+    cu_seqlens = _require_cuda_tensor(cu_seqlens, "cu_seqlens", torch.int32)
+    if packed_ids.dim() != 1 or cu_seqlens.dim() != 1 or cu_seqlens.shape[0] < 2:
+        raise ValueError("packed_ids must be [T] and cu_seqlens [N+1] with N >= 1")
+    total = packed_ids.shape[0]
+    if position_ids is None:
+        position_ids = positions_from_cu_seqlens(cu_seqlens, total)
+    position_ids = _require_cuda_tensor(position_ids, "position_ids", torch.int64)
+    if position_ids.shape != packed_ids.shape:
+        raise ValueError("position_ids must have the shape of packed_ids")
+    if int(max_seqlen) <= 0:
+        raise ValueError("max_seqlen must be positive")
+    binding = get_binding(model, params)
+    binding.check()
+    dev = packed_ids.device
+    n_seqs = cu_seqlens.shape[0] - 1
+    hidden = torch.empty(total, params.hidden_size, dtype=torch.bfloat16, device=dev) if return_hidden else None
+    if total == 0:
+        pooled = torch.zeros(n_seqs, params.hidden_size, dtype=torch.bfloat16, device=dev)
+        return (hidden, pooled) if return_hidden else pooled
+    pooled = torch.empty(n_seqs, params.hidden_size, dtype=torch.bfloat16, device=dev)
+    binding.run(packed_ids, cu_seqlens, position_ids, int(max_seqlen), hidden, pooled=pooled,
+                pool_mode=1 if pool == "mean" else 0, normalize=normalize)
+    binding.after_call()
+    return (hidden, pooled) if return_hidden else pooled
 
 
 def _varlen_forward(

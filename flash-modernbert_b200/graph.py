@@ -1,4 +1,4 @@
-"""Bucketed CUDA graphs for `packed_forward`, keyed on capacities.
+"""Bucketed CUDA graphs for `packed_forward` and for the padded `[B, S]` API, keyed on capacities.
 
 Role of packed_encoders/graph.py:44-74 (GraphConfig), 209-396 (packed runner) and
 435-472 (toggles). The reference keys a packed graph on `(M_bucket, N, Smax, backend)`,
@@ -22,7 +22,7 @@ from dataclasses import dataclass
 import torch
 from torch import Tensor, nn
 
-from . import forward
+from . import _lib, forward
 from .config import ModernBertParams
 from .locate import find_encoder
 from .state import get_state
@@ -161,6 +161,7 @@ class _PackedGraphRunner:
             self.eager_calls += 1
             return self._eager(packed_ids, cu_seqlens, max_seqlen, position_ids)
         binding = forward.get_binding(self._model, self._params)
+        binding.check()  # a fault recorded by the previous call (eager or replay) is raised here
         if int(max_seqlen) > binding.max_positions:
             self.eager_calls += 1  # the eager call grows the RoPE tables
             return self._eager(packed_ids, cu_seqlens, max_seqlen, position_ids)
@@ -180,7 +181,9 @@ class _PackedGraphRunner:
         m_real = captured.inputs.stage(packed_ids, cu_seqlens, position_ids)
         captured.graph.replay()
         self.replays += 1
-        return captured.out[:m_real].clone()
+        out = captured.out[:m_real].clone()
+        binding.after_call()  # the replayed kernels write the same status word as eager ones
+        return out
 
     def _eager(self, packed_ids, cu_seqlens, max_seqlen, position_ids):
         return forward.packed_forward(
@@ -267,6 +270,187 @@ class _PackedGraphRunner:
         return _PackedCaptured(graph=graph, inputs=static, out=out)
 
 
+# ---------------------------------------------------------------------------
+# Padded [B, S] runner (packed_encoders/graph.py:112-201)
+# ---------------------------------------------------------------------------
+
+
+@dataclass
+class _StaticInputs:
+    """Fixed-address `[B_cap, S_bucket]` inputs of one captured padded graph."""
+
+    input_ids: Tensor
+    attention_mask: Tensor
+
+    def stage(self, input_ids: Tensor, attention_mask: Tensor | None) -> None:
+        """Write a real `(b, s)` batch into the corner of the static buffers; everything
+        outside it is padding (mask 0), including the rows beyond `b`."""
+        b, s = input_ids.shape
+        self.input_ids.zero_()
+        self.input_ids[:b, :s] = input_ids
+        self.attention_mask.zero_()
+        if attention_mask is None:
+            self.attention_mask[:b, :s] = 1
+        else:
+            self.attention_mask[:b, :s] = (attention_mask != 0).to(self.attention_mask.dtype)
+
+
+@dataclass
+class _Captured:
+    graph: "torch.cuda.CUDAGraph"
+    inputs: _StaticInputs
+    out: Tensor
+    keep: tuple  # index / scratch tensors the graph's kernels write to
+
+
+class _GraphRunner:
+    """One captured graph per `(batch capacity, sequence bucket)` for `model(input_ids,
+    attention_mask)`, the role of packed_encoders/graph.py:112-201: one graph serves every
+    batch of at most `max_batch` rows whose width rounds up to the bucket.
+
+    The captured region is the whole padded call: mask -> `cu_seqlens` / indices (`_unpad`),
+    the gather of the real token ids, the packed forward at a capacity of `B_cap * S_bucket`
+    tokens, and the scatter back to `[B_cap, S_bucket, H]` with zero pad rows. The number of
+    real tokens never comes back to the host (the kernels read it and `cu_seqlens` on the
+    device), so a replay has no synchronisation in front of it, unlike the eager `_unpad`."""
+
+    def __init__(self, model: nn.Module, params: ModernBertParams, config: GraphConfig):
+        self._model = model
+        self._params = params
+        self._config = config
+        self._device = next(model.parameters()).device
+        self._cache: OrderedDict[tuple[int, int], _Captured] = OrderedDict()
+        self._workspace: Tensor | None = None
+        self._generation = -1
+        self.captures = 0
+        self.replays = 0
+        self.eager_calls = 0
+
+    def bucket_for(self, b: int, s: int) -> tuple[int, int] | None:
+        cfg = self._config
+        if cfg.max_seq is not None and s > cfg.max_seq:
+            return None
+        if cfg.max_batch is not None and b > cfg.max_batch:
+            return None
+        bb = b if cfg.max_batch is None else cfg.max_batch
+        sb = _round_up(s, cfg.pad_to)
+        if bb * sb > cfg.max_tokens or bb * sb <= 0:
+            return None
+        return bb, sb
+
+    def __call__(self, input_ids: Tensor, attention_mask: Tensor | None) -> Tensor:
+        b, s = input_ids.shape
+        key = self.bucket_for(b, s)
+        binding = forward.get_binding(self._model, self._params)
+        if key is None or key[1] > binding.max_positions:
+            self.eager_calls += 1
+            return self._eager(input_ids, attention_mask)
+        binding.check()
+        if binding.generation != self._generation:
+            self._cache.clear()
+            self._generation = binding.generation
+        captured = self._cache.get(key)
+        if captured is not None:
+            self._cache.move_to_end(key)
+        else:
+            captured = self._capture(*key)
+            self._insert(key, captured)
+        captured.inputs.stage(input_ids, attention_mask)
+        captured.graph.replay()
+        self.replays += 1
+        out = captured.out[:b, :s].clone()
+        binding.after_call()
+        return out
+
+    def _eager(self, input_ids: Tensor, attention_mask: Tensor | None) -> Tensor:
+        return forward.fused_forward(self._model, self._params, input_ids, attention_mask)
+
+    def _insert(self, key: tuple[int, int], captured: _Captured) -> None:
+        self._cache[key] = captured
+        while len(self._cache) > self._config.max_graphs:
+            self._cache.popitem(last=False)
+
+    def precapture(self, batch: int, seq_buckets) -> int:
+        binding = forward.get_binding(self._model, self._params)
+        self._generation = binding.generation
+        made = 0
+        for s in sorted({_round_up(int(v), self._config.pad_to) for v in seq_buckets}, reverse=True):
+            key = self.bucket_for(batch, s)
+            if key is not None and key[1] <= binding.max_positions and key not in self._cache:
+                self._insert(key, self._capture(*key))
+                made += 1
+        return made
+
+    def _capture(self, bb: int, sb: int) -> _Captured:
+        dev = self._device
+        lib = _lib.load()
+        binding = forward.get_binding(self._model, self._params)
+        binding.check()
+        cap = bb * sb
+        cfg = self._config
+        need = binding.workspace_bytes(cap, bb)
+        if cfg.max_batch is not None and cfg.max_seq is not None:
+            # the largest bucket this runner can ever capture: sized once, the arena never regrows
+            largest = min(cfg.max_batch * _round_up(cfg.max_seq, cfg.pad_to), cfg.max_tokens)
+            need = max(need, binding.workspace_bytes(largest, cfg.max_batch))
+        if self._workspace is None or self._workspace.numel() < need:
+            self._cache.clear()  # graphs captured so far hold the old arena's address
+            self._workspace = None
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        workspace = self._workspace
+        static = _StaticInputs(
+            input_ids=torch.zeros(bb, sb, dtype=torch.int64, device=dev),
+            attention_mask=torch.ones(bb, sb, dtype=torch.int64, device=dev),
+        )
+        hidden = self._params.hidden_size
+        seqlens = torch.zeros(bb, dtype=torch.int32, device=dev)
+        cu = torch.zeros(bb + 1, dtype=torch.int32, device=dev)
+        indices = torch.zeros(cap, dtype=torch.int64, device=dev)
+        positions = torch.zeros(cap, dtype=torch.int64, device=dev)
+        totals = torch.zeros(2, dtype=torch.int32, device=dev)
+        packed_ids = torch.zeros(cap, dtype=torch.int64, device=dev)
+        packed_out = torch.empty(cap, hidden, dtype=torch.bfloat16, device=dev)
+        out = torch.empty(bb, sb, hidden, dtype=torch.bfloat16, device=dev)
+        binding.refresh()
+
+        def run():
+            stream = _lib.current_stream_ptr()
+            positions.zero_()  # entries beyond the real count must stay inside the RoPE table
+            _lib.check(lib.pe_unpad_build(static.attention_mask.data_ptr(), 8, bb, sb, seqlens.data_ptr(),
+                                          cu.data_ptr(), indices.data_ptr(), positions.data_ptr(),
+                                          totals.data_ptr(), None, stream), "pe_unpad_build")
+            _lib.check(lib.pe_gather_rows_counted(static.input_ids.data_ptr(), indices.data_ptr(),
+                                                  totals.data_ptr(), cap, 8, packed_ids.data_ptr(), stream),
+                       "pe_gather_rows_counted")
+            binding.run(packed_ids, cu, positions, sb, packed_out, workspace=workspace, refresh=False)
+            _lib.check(lib.pe_repad_scatter_counted(packed_out.data_ptr(), indices.data_ptr(),
+                                                    totals.data_ptr(), cap, cap, hidden * 2,
+                                                    out.data_ptr(), stream), "pe_repad_scatter_counted")
+
+        with torch.no_grad(), torch.cuda.device(dev):
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(max(1, self._config.warmup)):
+                    run()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                run()
+        self.captures += 1
+        return _Captured(graph=graph, inputs=static, out=out,
+                         keep=(seqlens, cu, indices, positions, totals, packed_ids, packed_out))
+
+
+def build_runner(model: nn.Module, params: ModernBertParams, config: GraphConfig) -> _GraphRunner:
+    """The padded-API runner, with its `seq_buckets` captured now when `max_batch` says at which
+    batch capacity (packed_encoders/graph.py:410-427)."""
+    runner = _GraphRunner(model, params, config)
+    if config.seq_buckets and config.max_batch is not None:
+        runner.precapture(config.max_batch, config.seq_buckets)
+    return runner
+
+
 def build_packed_runner(model: nn.Module, params: ModernBertParams, config: GraphConfig,
                         backend: str | None = None) -> _PackedGraphRunner:
     del backend
@@ -295,6 +479,7 @@ def set_cuda_graph(model: object, enabled: bool, *, config: GraphConfig | None =
     if enabled and state.packed_graph_runner is None:
         encoder = find_encoder(model)
         state.packed_graph_runner = build_packed_runner(encoder, state.params, config or GraphConfig())
+        state.graph_runner = build_runner(encoder, state.params, config or GraphConfig())
     state.graph_enabled = bool(enabled)
 
 

@@ -22,6 +22,20 @@ def _bf16_cuda(t: Tensor, name: str) -> Tensor:
     return t if t.is_contiguous() else t.contiguous()
 
 
+def _index_cuda(t: Tensor, name: str, dtype: torch.dtype, like: Tensor) -> Tensor:
+    """An index operand (`cu_seqlens`, `position_ids`, token ids): the library reads it as raw
+    `dtype` data on the device of `like`, so anything else is refused here instead of being
+    misread there (an int64 `cu_seqlens` would give wrong boundaries, a CPU tensor a host
+    address inside a kernel)."""
+    if not isinstance(t, Tensor) or not t.is_cuda:
+        raise PackedEncodersError(f"{name} must be a CUDA tensor (this package has no CPU path)")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if t.device != like.device:
+        raise PackedEncodersError(f"{name} is on {t.device}, the data it indexes on {like.device}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
 class _Call:
     """Device guard + stream + status word for one library call."""
 
@@ -87,7 +101,7 @@ def fused_add_layer_norm(x: Tensor, residual: Tensor, weight: Tensor, eps: float
 def embed_layer_norm(ids: Tensor, table: Tensor, weight: Tensor, eps: float) -> Tensor:
     """`LN(table[ids])`: the embedding prologue of packed_encoders/forward.py:472-476."""
     table = _bf16_cuda(table, "table")
-    ids = ids.contiguous()
+    ids = _index_cuda(ids, "ids", torch.int64, table)
     out = torch.empty(ids.numel(), table.shape[1], dtype=torch.bfloat16, device=table.device)
     with _Call(table) as c:
         _lib.check(c.lib.pe_embed_ln(ids.data_ptr(), table.data_ptr(),
@@ -155,8 +169,9 @@ def rope_qk_inplace(qkv: Tensor, position_ids: Tensor, table: Tensor, n_heads: i
     if not qkv.is_contiguous():
         raise PackedEncodersError("qkv must be contiguous for the in-place rotation")
     qkv = _bf16_cuda(qkv, "qkv")
+    pos = _index_cuda(position_ids, "position_ids", torch.int64, qkv)
     with _Call(qkv) as c:
-        _lib.check(c.lib.pe_rope_qk_inplace(qkv.data_ptr(), position_ids.contiguous().data_ptr(),
+        _lib.check(c.lib.pe_rope_qk_inplace(qkv.data_ptr(), pos.data_ptr(),
                                             _bf16_cuda(table, "table").data_ptr(), table.shape[0],
                                             qkv.shape[0], n_heads,
                                             status_word(qkv.device).data_ptr(), c.stream),
@@ -169,11 +184,12 @@ def linear_qkv_rope(x: Tensor, wqkv: Tensor, position_ids: Tensor, table: Tensor
     x = _bf16_cuda(x, "x")
     wqkv = _bf16_cuda(wqkv, "wqkv")
     flat = x.reshape(-1, x.shape[-1])
+    pos = _index_cuda(position_ids, "position_ids", torch.int64, x)
     out = torch.empty(flat.shape[0], 3 * n_heads * 64, dtype=torch.bfloat16, device=x.device)
     with _Call(x) as c:
         _lib.check(c.lib.pe_gemm_qkv_rope_bf16(flat.data_ptr(), wqkv.data_ptr(), out.data_ptr(),
                                                flat.shape[0], n_heads, wqkv.shape[1],
-                                               position_ids.contiguous().data_ptr(),
+                                               pos.data_ptr(),
                                                _bf16_cuda(table, "table").data_ptr(), table.shape[0],
                                                status_word(x.device).data_ptr(), c.stream),
                    "pe_gemm_qkv_rope_bf16")
@@ -202,13 +218,14 @@ def attention_varlen_qkv(qkv: Tensor, cu_seqlens: Tensor, max_seqlen: int, n_hea
     """Varlen attention on the fused, already-rotated `qkv [T, 3*n_heads*64]`;
     `half_window=None` is full attention. Returns `[T, n_heads*64]`."""
     qkv = _bf16_cuda(qkv, "qkv")
+    cu = _index_cuda(cu_seqlens, "cu_seqlens", torch.int32, qkv)
     total = qkv.shape[0]
-    n_seqs = cu_seqlens.numel() - 1
+    n_seqs = cu.numel() - 1
     out = torch.empty(total, n_heads * 64, dtype=torch.bfloat16, device=qkv.device)
     with _Call(qkv) as c:
         ws_bytes = int(c.lib.pe_attn_workspace_bytes(total, n_seqs))
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=qkv.device)
-        _lib.check(c.lib.pe_attn_varlen(qkv.data_ptr(), cu_seqlens.contiguous().data_ptr(), n_seqs,
+        _lib.check(c.lib.pe_attn_varlen(qkv.data_ptr(), cu.data_ptr(), n_seqs,
                                         total, n_heads, -1 if half_window is None else half_window,
                                         int(max_seqlen), out.data_ptr(), ws.data_ptr(), ws_bytes,
                                         status_word(qkv.device).data_ptr(), c.stream),
@@ -224,11 +241,12 @@ def attention_varlen_qkv_static(qkv: Tensor, cu_seqlens: Tensor, max_seqlen: int
     calls share one built-in table, so keep them on one stream. Only the output tensor is
     created here, by the caller's own allocator."""
     qkv = _bf16_cuda(qkv, "qkv")
+    cu = _index_cuda(cu_seqlens, "cu_seqlens", torch.int32, qkv)
     total = qkv.shape[0]
     out = torch.empty(total, n_heads * 64, dtype=torch.bfloat16, device=qkv.device)
     with _Call(qkv) as c:
-        _lib.check(c.lib.pe_attn_varlen_static(qkv.data_ptr(), cu_seqlens.contiguous().data_ptr(),
-                                               cu_seqlens.numel() - 1, total, n_heads,
+        _lib.check(c.lib.pe_attn_varlen_static(qkv.data_ptr(), cu.data_ptr(),
+                                               cu.numel() - 1, total, n_heads,
                                                -1 if half_window is None else half_window,
                                                int(max_seqlen), out.data_ptr(),
                                                status_word(qkv.device).data_ptr(), c.stream),
@@ -245,9 +263,7 @@ def pool_packed(hidden: Tensor, cu_seqlens: Tensor, mode: str = "mean", normaliz
         raise ValueError(f"pool_packed: mode must be 'mean' or 'cls', got {mode!r}")
     hidden = _bf16_cuda(hidden, "hidden")
     total, width = hidden.shape
-    cu = cu_seqlens.contiguous()
-    if cu.dtype != torch.int32:
-        raise TypeError("pool_packed: cu_seqlens must be int32")
+    cu = _index_cuda(cu_seqlens, "cu_seqlens", torch.int32, hidden)
     n_seqs = cu.numel() - 1
     out = torch.empty(n_seqs, width, dtype=torch.bfloat16, device=hidden.device)
     with _Call(hidden) as c:

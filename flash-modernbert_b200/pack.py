@@ -20,7 +20,7 @@ from . import _lib
 from .config import ModernBertParams
 from .errors import PackedEncodersError
 from .forward import fused_forward, get_binding
-from .graph import GraphConfig, build_packed_runner, graphs_globally_disabled
+from .graph import GraphConfig, build_packed_runner, build_runner, graphs_globally_disabled
 from .locate import find_encoder
 from .state import ATTR, PatchState
 from .validate import validate as _validate
@@ -85,6 +85,7 @@ def _enable_graphs(encoder: nn.Module, state: PatchState, cuda_graph: bool | Gra
                    seq_cutoff: int | None) -> None:
     config = cuda_graph if isinstance(cuda_graph, GraphConfig) else GraphConfig(max_seq=seq_cutoff)
     state.packed_graph_runner = build_packed_runner(encoder, state.params, config)
+    state.graph_runner = build_runner(encoder, state.params, config)
     state.graph_enabled = True
 
 
@@ -126,7 +127,18 @@ def _make_forward(encoder: nn.Module, state: PatchState):
                 "they apply to plain bf16 inference under torch.no_grad().",
                 stacklevel=2,
             )
-        hidden = fused_forward(encoder, state.params, input_ids, attention_mask)
+        use_graph = (
+            wants_graph
+            and state.graph_runner is not None
+            and not torch.is_grad_enabled()
+            and not torch.is_autocast_enabled("cuda")
+            and input_ids.is_cuda
+            and input_ids.dim() == 2
+        )
+        if use_graph:
+            hidden = state.graph_runner(input_ids.to(torch.int64), attention_mask)
+        else:
+            hidden = fused_forward(encoder, state.params, input_ids, attention_mask)
         if not return_dict:
             return (hidden,)
         return BaseModelOutput(last_hidden_state=hidden)

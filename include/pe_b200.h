@@ -12,6 +12,18 @@
  * Each declaration names the function of pau-mensa/flash-modernbert
  * (package `packed_encoders`) whose work it takes over, as file:line.
  *
+ * Device status word (the `status` arguments): a kernel that has to give up writes the first
+ * such code there and carries on without touching memory it should not; 0 means none did.
+ * 101-103: a bounded wait inside a GEMM ran out; 201-204: inside an attention kernel;
+ * 301: token id outside the vocabulary (row 0 was used); 302: position outside the RoPE table
+ * (position 0 was used); 303: a cu_seqlens entry outside [0, T] or smaller than its predecessor
+ * (clamped into range: no kernel follows a boundary outside the caller's buffers).
+ *
+ * Inputs are expected to be finite.  The attention kernels fetch whole key/value tiles and mask
+ * the scores of keys outside a sequence to zero probability, so a NaN or Inf in one sequence's
+ * values can reach the rows of the sequences packed next to it (0 * NaN).  pe_forward_packed
+ * keeps the padding rows of a graph bucket finite by itself.
+ *
  * Tensors are row-major and contiguous unless a stride is named.  "bf16" is
  * __nv_bfloat16.  T = packed tokens, N = sequences, H = hidden size,
  * nh = heads, D = head dim (64 only), I = GeGLU intermediate size.
@@ -79,21 +91,11 @@ int pe_device_check(void);
 /* key 2 (PE_OPT_FUSED_ROPE, default 1): Wqkv and RoPE as one kernel (1) or as pe_gemm_bf16_tn
  * followed by pe_rope_qk_inplace (0). */
 #define PE_OPT_FUSED_ROPE 2
-/* key 3 (PE_OPT_LOCAL_ATTN_SINGLE_PASS, default 1): sliding-window layers of long batches use the
- * one-pass tensor-memory kernel (1) or the generic online-softmax one (0). */
-#define PE_OPT_LOCAL_ATTN_SINGLE_PASS 3
 /* key 4 (PE_OPT_FUSED_RESIDUAL, default 1): Wo and the MLP's Wo add their result to the residual
  * stream in the GEMM epilogue and the norms run as plain LayerNorms (1), or the projections are
  * materialised and pe_add_ln adds them (0). */
 #define PE_OPT_FUSED_RESIDUAL 4
-/* key 5 (PE_OPT_ATTN_TWO_CTA, default 1): full-attention layers of long batches use the kernel
-   that keeps two CTAs per SM and the output accumulator in tensor memory (1), or the
-   one-CTA-per-SM kernel with eight softmax warps (0). */
-#define PE_OPT_ATTN_TWO_CTA 5
-/* key 6 (PE_OPT_LOCAL_ATTN_TWO_CTA, default 1): sliding-window layers (half window 64) of long
-   batches use the kernel that keeps two CTAs per SM and S, P and O in place in tensor memory (1),
-   or the one-CTA-per-SM kernels selected by key 3 (0). */
-#define PE_OPT_LOCAL_ATTN_TWO_CTA 6
+/* A forward reads the switches once, when it starts to enqueue its kernels. */
 int pe_set_option(int key, int value);
 
 /* ---- padding boundary ------------------------------------------------------ */
@@ -121,6 +123,18 @@ int pe_gather_rows(const void* src, const int64_t* indices, int64_t T, int64_t r
  * writes them); every output row is written exactly once. */
 int pe_repad_scatter(const void* packed, const int64_t* indices, int64_t T, int64_t rows_out,
                      int64_t row_bytes, void* out, void* stream);
+
+/* pe_gather_rows and pe_repad_scatter for a caller that has not read the row count back to the
+ * host: the padded API inside a captured CUDA graph, where pe_unpad_build (totals_host = NULL)
+ * leaves T in totals_dev[0] and the synchronising read of packed_encoders/forward.py:397-402
+ * (int(seqlens.max())) would end the capture.  The count is read on the device from *count_dev
+ * and clamped to `capacity` (the rows the buffers hold).  Gather: rows at or beyond the count are
+ * written as zeros, their indices are not read.  Scatter: only indices[0 .. count) are searched. */
+int pe_gather_rows_counted(const void* src, const int64_t* indices, const int32_t* count_dev,
+                           int64_t capacity, int64_t row_bytes, void* dst, void* stream);
+int pe_repad_scatter_counted(const void* packed, const int64_t* indices, const int32_t* count_dev,
+                             int64_t capacity, int64_t rows_out, int64_t row_bytes, void* out,
+                             void* stream);
 
 /* ---- tails (memory-bound) -------------------------------------------------- */
 
@@ -225,7 +239,7 @@ int pe_attn_varlen(const void* qkv, const int32_t* cu_seqlens, int n_seqs, int64
 /* pe_attn_varlen for callers that must not allocate device memory and have none to lend: a
  * plug-in hosted by a process whose own allocator already holds the whole GPU, or a serving
  * thread with a frozen memory budget that may not call cudaMalloc (which can stall the device)
- * on its request path.  No counterpart in the reference.  The tile table lives in a 1.1 MB
+ * on its request path.  No counterpart in the reference.  The tile table lives in a 1.2 MB
  * array inside the library (every GPU that loads the library holds it until exit), so the
  * call takes no workspace and calls no allocator.  Limits: n_seqs <= 4096 and T <= 1,048,576,
  * beyond which it returns PE_ERR_WORKSPACE.  The first call on each device looks the array's
@@ -247,11 +261,25 @@ size_t pe_forward_workspace_bytes(const pe_model* model, int64_t T, int n_seqs);
  * beyond cu_seqlens[n_seqs] (graph-bucket padding) run through the GEMMs and
  * tails but attend to nothing, as in packed_encoders/graph.py:244-248.
  * status: device int32, must be zero on entry; a kernel that gives up on a bounded
- * wait or meets an out-of-range id/position writes a non-zero code there. */
+ * wait or meets an out-of-range id / position / boundary writes a non-zero code there. */
 int pe_forward_packed(const pe_model* model, const int64_t* ids, const int32_t* cu_seqlens,
                       const int64_t* position_ids, int64_t T, int n_seqs, int max_seqlen,
                       void* workspace, size_t workspace_bytes, void* out, int32_t* status,
                       void* stream);
+
+/* pe_forward_packed with the pooling head fused into the final LayerNorm, for callers that turn
+ * the hidden state into one embedding per sequence right away
+ * (benchmarks/showcases/inference.py:193-209 of the reference: packed_forward, fp32 segment mean
+ * by index_add_, F.normalize).  pooled_out: bf16 [n_seqs, H] = per sequence the first token's row
+ * (pool_mode 0) or the fp32 mean of its rows (pool_mode 1) of the bf16 last hidden state, divided
+ * by max(||.||_2, 1e-12) if normalize != 0, rounded to bf16 last; zero-length sequences give zero
+ * rows.  hidden_out: bf16 [T, H] or NULL; with NULL the hidden state is never written (and with
+ * pool_mode 0 the final LayerNorm runs on one row per sequence only).  Same workspace size as
+ * pe_forward_packed.  Fixed summation order: repeated calls are bit-identical. */
+int pe_forward_packed_pooled(const pe_model* model, const int64_t* ids, const int32_t* cu_seqlens,
+                             const int64_t* position_ids, int64_t T, int n_seqs, int max_seqlen,
+                             void* workspace, size_t workspace_bytes, int pool_mode, int normalize,
+                             void* hidden_out, void* pooled_out, int32_t* status, void* stream);
 
 /* Copies the device status word to the host and synchronises the stream.
  * Returns PE_OK if it is zero, else PE_ERR_DEVICE with *code_out = the word. */

@@ -152,20 +152,73 @@ def test_full_size_properties(pe, cuda_device):
     assert float((out.float() - 0.5).abs().max()) < 4e-3
 
 
-@pytest.mark.parametrize("half_window,key", [(None, 5), (64, 6)])
-def test_one_cta_kernels_behind_their_options_agree(pe, cuda_device, half_window, key):
-    """`pe_set_option(5, 0)` / `(6, 0)` select the one-CTA-per-SM kernels; both generations must
-    agree with the reference and with each other to within P's bf16 rounding."""
-    from flash_modernbert_b200 import _lib
+@pytest.mark.parametrize("half_window", [None, 64])
+def test_mixed_window_of_queries_and_documents(pe, cuda_device, half_window):
+    """A serving window that mixes ~30-token queries with documents
+    (benchmarks/showcases/mixed_serving.py:151-193 of the reference): the schedule sends the
+    sequences of at most 64 tokens to the register-tiled kernel and the rest to the tensor-memory
+    kernels, inside one call. Checked against the fp32 reference, and the queries' rows are
+    bit-equal to the same queries encoded without the documents."""
+    lengths = [30, 700, 8, 48, 129, 64, 65, 17, 2048, 41, 1, 300, 33]
+    qkv, cu = _qkv(lengths, 4, cuda_device, seed=21)
+    out = _run(qkv, cu, 4, half_window, cuda_device)
+    _check(out, qkv, cu, half_window, f"mixed window={half_window}")
+    short = [i for i, n in enumerate(lengths) if n <= 64]
+    bounds = cu.tolist()
+    rows = torch.cat([torch.arange(bounds[i], bounds[i + 1]) for i in short])
+    q_short = qkv[rows]
+    cu_short = torch.zeros(len(short) + 1, dtype=torch.int32)
+    cu_short[1:] = torch.tensor([lengths[i] for i in short]).cumsum(0)
+    alone = _run(q_short, cu_short, 4, half_window, cuda_device, max_seqlen=64)
+    assert torch.equal(out[rows.to(cuda_device)], alone)
 
-    qkv, cu = _qkv([700, 129, 300, 2048], 4, cuda_device, seed=7)
+
+def test_bad_cu_seqlens_is_clamped_and_reported(pe, cuda_device):
+    """A cu_seqlens whose entries run past the T given to the call (or backwards) must not make
+    any kernel leave the caller's buffers: the schedule clamps the boundaries, the call reports
+    status 303, and rows at or beyond T stay untouched. qkv and out are allocated for the larger
+    claimed count, so that even an unguarded kernel would stay inside its own allocations."""
+    from flash_modernbert_b200 import _lib, ops
+
     lib = _lib.load()
-    new = _run(qkv, cu, 4, half_window, cuda_device)
-    try:
-        assert lib.pe_set_option(key, 0) == 0
-        old = _run(qkv, cu, 4, half_window, cuda_device)
-    finally:
-        lib.pe_set_option(key, 1)
-    _check(old, qkv, cu, half_window, f"one-CTA kernel, window={half_window}")
-    _check(new, qkv, cu, half_window, f"two-CTA kernel, window={half_window}")
-    assert float((old.float() - new.float()).abs().max()) < 0.02
+    nh, claimed, given = 2, 1024, 640
+    gen = torch.Generator().manual_seed(3)
+    qkv = torch.randn(claimed, 3 * nh * 64, generator=gen).to(torch.bfloat16).to(cuda_device)
+    for cu_list in ([0, 300, 700, 1024], [0, 500, 400, 640], [-5, 200, 640, 640]):
+        cu = torch.tensor(cu_list, dtype=torch.int32, device=cuda_device)
+        out = torch.full((claimed, nh * 64), 7.0, dtype=torch.bfloat16, device=cuda_device)
+        status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+        ws_bytes = int(lib.pe_attn_workspace_bytes(given, len(cu_list) - 1))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=cuda_device)
+        rc = lib.pe_attn_varlen(qkv.data_ptr(), cu.data_ptr(), len(cu_list) - 1, given, nh, -1, 512,
+                                out.data_ptr(), ws.data_ptr(), ws_bytes, status.data_ptr(),
+                                _lib.current_stream_ptr())
+        assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        assert int(status.item()) == 303, (cu_list, int(status.item()))
+        assert bool((out[given:] == 7.0).all()), cu_list           # nothing written past T
+        assert bool(torch.isfinite(out[:given].float()).all())
+    # a consistent table reports nothing
+    cu = torch.tensor([0, 300, 640], dtype=torch.int32, device=cuda_device)
+    status.zero_()
+    out = ops.attention_varlen_qkv(qkv[:given].contiguous(), cu, 340, nh, None)
+    ops.check_status(cuda_device)
+
+
+def test_index_operands_are_validated(pe, cuda_device):
+    """int64 cu_seqlens, CPU position_ids and the like are refused before any kernel sees them."""
+    from flash_modernbert_b200 import ops
+
+    qkv = torch.zeros(16, 3 * 64, dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(ValueError, match="int32"):
+        ops.attention_varlen_qkv(qkv, torch.tensor([0, 16], device=cuda_device), 16, 1, None)
+    with pytest.raises(pe.PackedEncodersError, match="CUDA"):
+        ops.attention_varlen_qkv(qkv, torch.tensor([0, 16], dtype=torch.int32), 16, 1, None)
+    table = ops.rope_table(10000.0, 64, cuda_device)
+    with pytest.raises(pe.PackedEncodersError, match="CUDA"):
+        ops.rope_qk_inplace(qkv, torch.arange(16), table, 1)
+    with pytest.raises(ValueError, match="int64"):
+        ops.rope_qk_inplace(qkv, torch.arange(16, dtype=torch.int32, device=cuda_device), table, 1)
+    emb = torch.zeros(32, 64, dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(ValueError, match="int64"):
+        ops.embed_layer_norm(torch.zeros(4, dtype=torch.int32, device=cuda_device), emb, emb[0], 1e-5)

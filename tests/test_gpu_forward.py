@@ -271,6 +271,66 @@ def test_against_reference_gpu_packed_forward(pe, cuda_device, base_models):
         sys.path.remove(str(ref_dir))
 
 
+def _token_cosines(a: torch.Tensor, b: torch.Tensor):
+    """Per-token cosine and max-abs of two [T, H] tensors, computed on their device in fp32."""
+    worst, max_abs = 1.0, 0.0
+    for start in range(0, a.shape[0], 65536):
+        x = a[start:start + 65536].float()
+        y = b[start:start + 65536].float()
+        cos = (x * y).sum(-1) / (x.norm(dim=-1) * y.norm(dim=-1)).clamp_min(1e-12)
+        worst = min(worst, float(cos.min()))
+        max_abs = max(max_abs, float((x - y).abs().max()))
+    return worst, max_abs
+
+
+def test_cfg3_headline_size_against_reference_gpu_and_hf_eager(pe, cuda_device, base_models):
+    """The headline workload at full size (512 documents up to 8,192 tokens, 306,851 tokens): all
+    tokens against the reference's own GPU packed_forward (the relation of the reference's
+    tests/test_varlen.py:328-381, on the seeded random-init weights), and one whole long document
+    (4,000 - 8,192 tokens: dozens of key tiles per query tile) taken out of that batch against
+    Hugging Face eager fp32 on the host."""
+    from flash_modernbert_b200 import forward
+
+    cpu, gpu = base_models
+    wl = S.workload("cfg3").sorted_by_length()
+    ids, cu, max_s, pos = _packed_inputs(wl, cuda_device)
+    cfg = gpu.config
+    if not hasattr(cfg, "global_attn_every_n_layers"):
+        cfg.global_attn_every_n_layers = 3
+    params = pe.ModernBertParams.from_hf_config(cfg)
+    out = pe.packed_forward(gpu, params, ids, cu, max_s, pos)
+    forward.get_binding(gpu, params).check(sync=True)
+
+    # one whole document between 4,000 and 8,192 tokens, against HF eager fp32
+    n = max(i for i, length in enumerate(wl.lengths) if length >= 4000)   # the shortest such (sorted descending)
+    s, e = int(cu[n]), int(cu[n + 1])
+    ref_doc = O.hf_eager_packed(cpu, [wl.sequences()[n]])
+    rep = O.cosine_report(out[s:e].cpu(), ref_doc)
+    print(f"cfg3 document of {e - s} tokens vs HF eager fp32: {rep}")
+    assert rep["min_token_cos"] >= COS_GATE, rep
+
+    ref_dir = ROOT / "baseline" / "_ref"
+    if not (ref_dir / "packed_encoders").exists():
+        pytest.skip("reference install not present (HF eager part passed)")
+    sys.path.insert(0, str(ref_dir))
+    try:
+        try:
+            from packed_encoders import forward as ref_forward
+            from packed_encoders.config import ModernBertParams as RefParams
+            with torch.no_grad():
+                ref_out = ref_forward.packed_forward(gpu, RefParams.from_hf_config(cfg), ids, cu, max_s, pos)
+            torch.cuda.synchronize()
+        except Exception as exc:  # noqa: BLE001
+            pytest.skip(f"reference packed_forward does not run here: {type(exc).__name__}: {exc}")
+        assert ref_out.shape == out.shape == (306851, 768)
+        worst, max_abs = _token_cosines(out, ref_out)
+        print(f"cfg3 (306,851 tokens) vs reference GPU packed_forward: min per-token cosine {worst:.6f}, "
+              f"max-abs {max_abs:.4f}")
+        assert worst >= COS_GATE, (worst, max_abs)
+    finally:
+        sys.path.remove(str(ref_dir))
+
+
 def _subset(wl, picks):
     seqs = wl.sequences()
     return [seqs[i] for i in picks]
@@ -278,6 +338,7 @@ def _subset(wl, picks):
 
 @pytest.mark.parametrize("arch,config,picks", [
     ("large", "cfg4", [5, 40]),          # two long documents (2,048..8,192 tokens) on ModernBERT-large
+    ("large", "cfg4", "shortest"),       # one whole document of cfg4 (>= 2,048 tokens), not truncated
     ("1b", "cfg5", [3, 100, 9000]),      # two queries and one document on the 1B-class model
 ])
 def test_other_architectures_against_hf_eager(pe, cuda_device, arch, config, picks):
@@ -286,8 +347,11 @@ def test_other_architectures_against_hf_eager(pe, cuda_device, arch, config, pic
     from flash_modernbert_b200 import forward
 
     wl = S.workload(config)
-    seqs = _subset(wl, picks)
-    seqs = [s[:2000] for s in seqs]       # bound the CPU side of the check
+    if picks == "shortest":
+        seqs = _subset(wl, [min(range(len(wl.lengths)), key=lambda i: wl.lengths[i])])
+        assert seqs[0].numel() >= 2048
+    else:
+        seqs = [s[:2000] for s in _subset(wl, picks)]       # bound the CPU side of the check
     cpu = S.make_model(arch)
     gpu = S.make_model(arch, dtype=torch.bfloat16, device=cuda_device)
     params = pe.ModernBertParams.from_hf_config(gpu.config)
@@ -378,3 +442,153 @@ def test_graphs_precaptured_at_pack_time(pe, cuda_device, tiny_models):
         assert runner.captures == 2 and runner.replays == 3      # nothing captured lazily
     finally:
         pe.unpack(gpu)
+
+
+def _padded(seqs, b_cols=None):
+    b, s = len(seqs), b_cols or max(x.numel() for x in seqs)
+    ids = torch.zeros(b, s, dtype=torch.int64)
+    mask = torch.zeros(b, s, dtype=torch.int64)
+    for i, seq in enumerate(seqs):
+        ids[i, : seq.numel()] = seq
+        mask[i, : seq.numel()] = 1
+    return ids, mask
+
+
+def test_padded_api_through_cuda_graphs(pe, cuda_device, tiny_models):
+    """`model(input_ids, attention_mask)` with `cuda_graph=GraphConfig(...)`: what the reference's
+    tests/test_graph_bucketing.py:102-234 pins for its rectangular runner - one graph for every
+    batch size up to max_batch, the max_seq cut-off, the LRU bound, pre-capture of seq_buckets
+    at pack() time, and replay equal to the eager forward."""
+    _, _, gpu, vocab = tiny_models
+    cfg = pe.GraphConfig(pad_to=64, max_batch=8, max_seq=200, max_graphs=2, seq_buckets=(64,))
+    pe.pack(gpu, validate=False, cuda_graph=cfg)
+    try:
+        state = pe.get_state(gpu)
+        runner = state.graph_runner
+        assert runner.captures == 1 and list(runner._cache) == [(8, 64)]       # captured inside pack()
+        gen = torch.Generator().manual_seed(5)
+
+        def batch(n, lo, hi):
+            lengths = torch.randint(lo, hi, (n,), generator=gen).tolist()
+            return _padded([torch.randint(5, vocab, (l,), generator=gen) for l in lengths])
+
+        def both(ids, mask):
+            with torch.no_grad():
+                graphed = gpu(input_ids=ids.to(cuda_device), attention_mask=mask.to(cuda_device)).last_hidden_state
+                with pe.no_cuda_graph(gpu):
+                    eager = gpu(input_ids=ids.to(cuda_device), attention_mask=mask.to(cuda_device)).last_hidden_state
+            return graphed, eager
+
+        for n in (1, 3, 8):                                   # one graph for all b <= max_batch
+            ids, mask = batch(n, 20, 60)
+            graphed, eager = both(ids, mask)
+            assert graphed.shape == eager.shape == (n, ids.shape[1], 256)
+            assert torch.equal(graphed, eager)                # same kernels on the same rows
+            assert not bool(graphed[~mask.bool().to(cuda_device)].ne(0).any())   # pad rows exactly zero
+        assert runner.captures == 1 and runner.replays == 3
+        ids, mask = batch(4, 70, 128)                         # the 128 bucket: tensor-memory attention
+        graphed, eager = both(ids, mask)
+        assert torch.equal(graphed, eager) and runner.captures == 2
+        ids, mask = batch(2, 130, 190)                        # a third bucket evicts the oldest
+        graphed, eager = both(ids, mask)
+        assert torch.equal(graphed, eager)
+        assert runner.captures == 3 and list(runner._cache) == [(8, 128), (8, 192)]
+        before = runner.eager_calls
+        ids, mask = batch(2, 201, 260)                        # over max_seq: eager
+        both(ids, mask)
+        assert runner.eager_calls == before + 1
+        ids, mask = batch(9, 20, 60)                          # over max_batch: eager
+        both(ids, mask)
+        assert runner.eager_calls == before + 2
+        with torch.no_grad():                                  # no mask: every row is a full sequence
+            nomask = gpu(input_ids=ids[:3, :16].to(cuda_device)).last_hidden_state
+            with pe.no_cuda_graph(gpu):
+                nomask_eager = gpu(input_ids=ids[:3, :16].to(cuda_device)).last_hidden_state
+        assert torch.equal(nomask, nomask_eager)
+        replays = runner.replays
+        gpu(input_ids=ids[:3, :16].to(cuda_device))           # autograd on: eager
+        assert runner.replays == replays
+    finally:
+        pe.unpack(gpu)
+
+
+def test_graph_replay_reports_a_bad_token_id(pe, cuda_device, tiny_models):
+    """A token id outside the vocabulary fed through a graph replay is reported like in the eager
+    path: on the same call with PE_B200_CHECK_STATUS=1, else on the next one."""
+    from flash_modernbert_b200 import _lib
+
+    _, _, gpu, vocab = tiny_models
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    pe.pack(gpu, validate=False, cuda_graph=pe.GraphConfig(pad_to=64, max_batch=4, max_seq=64))
+    try:
+        good = pe.pack_sequences([torch.arange(5, 25), torch.arange(30, 60)], device=cuda_device)
+        bad_ids = good.input_ids.clone()
+        bad_ids[3] = vocab + 7
+        with torch.no_grad():
+            pe.packed_forward(gpu, params, *good.forward_args())                  # capture + replay
+            pe.packed_forward(gpu, params, bad_ids, good.cu_seqlens, good.max_seqlen, good.position_ids)
+            torch.cuda.synchronize()
+            with pytest.raises(_lib.NativeLibraryError, match="301"):
+                pe.packed_forward(gpu, params, *good.forward_args())              # raised on the next call
+            os.environ["PE_B200_CHECK_STATUS"] = "1"
+            try:
+                with pytest.raises(_lib.NativeLibraryError, match="301"):
+                    pe.packed_forward(gpu, params, bad_ids, good.cu_seqlens, good.max_seqlen, good.position_ids)
+            finally:
+                del os.environ["PE_B200_CHECK_STATUS"]
+            assert pe.get_state(gpu).packed_graph_runner.replays >= 3
+            pe.packed_forward(gpu, params, *good.forward_args())                  # the word was cleared
+    finally:
+        pe.unpack(gpu)
+
+
+def test_non_finite_bucket_padding_never_reaches_real_rows(pe, cuda_device, tiny_models):
+    """Graph buckets pad the token dimension; the padding rows of the scratch arena hold whatever
+    the previous user of that memory left. With sequences longer than 64 tokens (the tensor-memory
+    attention kernels, which fetch whole key/value tiles) a non-finite pattern there must not
+    turn the last real sequence into NaN: real rows are bit-equal to the eager run."""
+    _, _, gpu, vocab = tiny_models
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    pe.pack(gpu, validate=False, cuda_graph=pe.GraphConfig(pad_to=1024, max_batch=8, max_seq=512))
+    try:
+        runner = pe.get_state(gpu).packed_graph_runner
+        gen = torch.Generator().manual_seed(13)
+        seqs = [torch.randint(5, vocab, (l,), generator=gen) for l in (200, 77, 130, 45, 301)]
+        batch = pe.pack_sequences(seqs, device=cuda_device)      # 753 tokens in a 1,024 bucket
+        with torch.no_grad():
+            first = pe.packed_forward(gpu, params, *batch.forward_args())
+            runner._workspace.fill_(0xFF)                        # bf16 0xFFFF is a NaN
+            poisoned = pe.packed_forward(gpu, params, *batch.forward_args())
+            with pe.no_cuda_graph(gpu):
+                eager = pe.packed_forward(gpu, params, *batch.forward_args())
+        assert runner.replays == 2
+        assert bool(torch.isfinite(poisoned.float()).all())
+        assert torch.equal(poisoned, eager) and torch.equal(first, eager)
+    finally:
+        pe.unpack(gpu)
+
+
+def test_mixed_serving_window_matches_split_batches(pe, cuda_device, tiny_models):
+    """A window holding queries and documents together (benchmarks/showcases/mixed_serving.py:151-193:
+    `unified_packed`) gives every request the embedding it gets when queries and documents are
+    encoded as two separate batches, as the reference's split baseline does."""
+    _, _, gpu, vocab = tiny_models
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    gen = torch.Generator().manual_seed(17)
+    kinds = ["query"] * 12 + ["document"] * 12
+    lengths = torch.randint(8, 49, (12,), generator=gen).tolist() + torch.randint(65, 400, (12,), generator=gen).tolist()
+    seqs = [torch.randint(5, vocab, (l,), generator=gen) for l in lengths]
+    windows = pe.mixed_windows(kinds, lengths, requests_per_window=8, query_fraction=0.5, windows=3, seed=1)
+    assert all(sum(kinds[i] == "query" for i in w) == 4 and len(set(w)) == 8 for w in windows)
+    for chosen in windows:
+        window, pooled = pe.encode_window(gpu, params, [seqs[i] for i in chosen], chosen,
+                                          [kinds[i] for i in chosen], pool="mean")
+        assert window.requests == chosen and pooled.shape == (8, 256)
+        for kind in ("query", "document"):
+            slots = [n for n, i in enumerate(chosen) if kinds[i] == kind]
+            _, split = pe.encode_window(gpu, params, [seqs[chosen[n]] for n in slots], pool="mean")
+            assert float((pooled[slots].float() - split.float()).abs().max()) <= 2.0 ** -7
+    # arrival-order windows sized for graph buckets: nothing reordered, budgets respected
+    plan = pe.plan_windows(lengths, token_buckets=(512, 2048), max_sequences=8)
+    assert [i for w in plan for i in w] == list(range(len(lengths)))
+    assert all(sum(lengths[i] for i in w) <= 2048 or len(w) == 1 for w in plan) and all(len(w) <= 8 for w in plan)

@@ -108,3 +108,21 @@ def test_fused_residual_equals_two_steps(pe, cuda_device, m, n, k):
     assert ops.linear_residual(a_d, w_d, inplace, inplace=True).data_ptr() == inplace.data_ptr()
     ops.check_status(cuda_device)
     assert torch.equal(inplace, expected)
+
+
+@pytest.mark.parametrize("m,n,k", [(40961, 768, 768), (45000, 768, 1152)])
+def test_inplace_residual_with_several_tiles_per_cta(pe, cuda_device, m, n, k):
+    """More output tiles than CTAs (321 x 3 or 352 x 3 tiles on 148 SMs): every CTA owns
+    several tiles, so the epilogue's chain that fetches the first block of X for the NEXT tile
+    while finishing this one is live, and X is overwritten in place while other CTAs still read
+    their own blocks. Bit-exact against the two-step form."""
+    from flash_modernbert_b200 import ops
+
+    a, w, a_d, w_d = _inputs(m, n, k, cuda_device, seed=11)
+    res = torch.randn(m, n, generator=torch.Generator().manual_seed(12)).to(torch.bfloat16).to(cuda_device)
+    expected = res + ops._linear(a_d, w_d)
+    inplace = res.clone()
+    ops.linear_residual(a_d, w_d, inplace, inplace=True)
+    ops.check_status(cuda_device)
+    assert torch.equal(inplace, expected)
+    assert torch.equal(ops.linear_residual(a_d, w_d, res), expected)

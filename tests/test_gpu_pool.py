@@ -93,3 +93,36 @@ def test_project_normalize_against_oracle(pe, cuda_device, out_features, rows):
     assert float((got - ref).abs().max()) <= 2.0 ** -7
     rep = O.cosine_report(got, ref)
     assert rep["min_token_cos"] > 0.9999, rep
+
+
+@pytest.mark.parametrize("pool", ["mean", "cls"])
+@pytest.mark.parametrize("normalize", [True, False])
+def test_forward_with_the_pooling_head_fused_into_the_final_norm(pe, cuda_device, pool, normalize):
+    """`packed_forward_pooled` (one library call; the pooling runs inside the final LayerNorm and
+    the hidden state is not written) against `packed_forward` followed by `pool_packed`, i.e. what
+    benchmarks/showcases/inference.py:193-209 of the reference does in three torch ops. The
+    hidden state it can return as well is bit-equal to `packed_forward`'s; the embeddings agree
+    to one bf16 step (the fp32 sums run in a different, fixed order)."""
+    from flash_modernbert_b200 import forward, ops
+    from oracle import synthetic as S
+
+    vocab = 1024
+    gpu = S.make_model("tiny", vocab, dtype=torch.bfloat16, device=cuda_device)
+    wl = S.workload("tiny_mixed", vocab)
+    params = pe.ModernBertParams.from_hf_config(gpu.config)
+    batch = pe.pack_sequences(wl.sequences(), device=cuda_device)
+    hidden = pe.packed_forward(gpu, params, *batch.forward_args())
+    expected = ops.pool_packed(hidden, batch.cu_seqlens, pool, normalize)
+    got = pe.packed_forward_pooled(gpu, params, *batch.forward_args(), pool=pool, normalize=normalize)
+    both_hidden, both = pe.packed_forward_pooled(gpu, params, *batch.forward_args(), pool=pool,
+                                                 normalize=normalize, return_hidden=True)
+    forward.get_binding(gpu, params).check(sync=True)
+    assert got.shape == expected.shape == (len(wl.lengths), 256)
+    assert torch.equal(both_hidden, hidden)
+    scale = float(expected.float().abs().max())
+    for emb in (got, both):
+        assert float((emb.float() - expected.float()).abs().max()) <= scale * 2.0 ** -7
+    if pool == "cls":
+        assert torch.equal(got, expected)          # no summation involved: same bits
+    again = pe.packed_forward_pooled(gpu, params, *batch.forward_args(), pool=pool, normalize=normalize)
+    assert torch.equal(again, got)                 # fixed summation order

@@ -169,7 +169,8 @@ def test_graph_runner_lru_with_fakes(pe, monkeypatch):
     runner._generation = 0
     runner.captures = runner.replays = runner.eager_calls = 0
     monkeypatch.setattr(forward, "get_binding",
-                        lambda m, p: SimpleNamespace(max_positions=8192, generation=0))
+                        lambda m, p: SimpleNamespace(max_positions=8192, generation=0,
+                                                     check=lambda: None, after_call=lambda: None))
     captured_keys = []
 
     def fake_capture(token_cap, seq_cap, rows):
@@ -227,8 +228,14 @@ def test_shard_plan_balances_and_restores(pe):
         assert np.array_equal(seen, np.arange(len(lengths)))       # every sequence exactly once
         loads = np.asarray([costs[g].sum() for g in plan.groups])
         assert loads.max() / loads.mean() < 1.02                    # cost-balanced within 2 %
-        assert np.unique(plan.restore_index).size == plan.total_tokens
-        assert plan.restore_index.max() < world * plan.max_tokens
+        restore = plan.restore_index()
+        assert np.array_equal(np.sort(restore), np.arange(plan.total_tokens))   # a permutation of the rows
+        # each rank's rows are one contiguous range of the gathered tensor
+        for r, g in enumerate(plan.groups):
+            rows = np.sort(np.concatenate([plan.seq_rows[i] + np.arange(lengths[i]) for i in g]))
+            assert rows[0] == plan.row_start[r] and rows[-1] == plan.row_start[r + 1] - 1
+            assert np.array_equal(rows, np.arange(rows[0], rows[-1] + 1))
+        assert np.array_equal(plan.order[plan.seq_slot], np.arange(len(lengths)))
     # the FLOP model's local-layer pair count (129 s - 4160 beyond 65 tokens)
     assert shard.local_pairs(np.array([10, 65, 66, 1000])).tolist() == [100, 4225, 4354, 124840]
     with pytest.raises(ValueError):

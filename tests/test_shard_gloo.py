@@ -36,7 +36,14 @@ def _worker(rank: int, world: int, port: int, lengths, result_dir: str):
         # stand-in encoder: row t = [id, 2*id, rank]
         local_out = torch.stack([local_ids.float(), 2 * local_ids.float(),
                                  torch.full_like(local_ids, rank).float()], dim=1)
-        full = shard.gather_embeddings(local_out, plan)
+        ranked = shard.gather_embeddings(local_out, plan)          # rank-major: no permutation
+        assert ranked.shape == (total, 3)
+        for i, n in enumerate(lengths):
+            rows = ranked[plan.seq_rows[i]:plan.seq_rows[i] + n]
+            assert torch.equal(rows[:, 0], seqs[i].float())
+        assert np.array_equal(plan.gathered_cu_seqlens(),
+                              np.concatenate(([0], np.cumsum(np.asarray(lengths)[plan.order]))))
+        full = shard.gather_embeddings(local_out, plan, restore=True)
         assert full.shape == (total, 3)
         assert torch.equal(full[:, 0], ids.float()) and torch.equal(full[:, 1], 2 * ids.float())
         owners = np.empty(total, dtype=np.int64)
@@ -55,6 +62,8 @@ def _worker(rank: int, world: int, port: int, lengths, result_dir: str):
         for r, g in enumerate(plan.groups):
             seq_owner[np.asarray(g, dtype=np.int64)] = r
         assert np.array_equal(all_pooled[:, 1].numpy().astype(np.int64), seq_owner)
+        ranked_pooled = shard.gather_pooled(pooled, plan, restore=False)
+        assert torch.equal(ranked_pooled[:, 0], torch.tensor(starts[:-1][plan.order], dtype=torch.float32))
         with open(os.path.join(result_dir, f"ok{rank}"), "w") as f:
             f.write("ok")
     finally:
@@ -74,7 +83,7 @@ def test_single_rank_is_identity():
     plan = shard.plan_shards([4, 2, 6], 1)
     seqs = list(torch.split(torch.arange(12), [4, 2, 6]))
     local = torch.cat(shard.local_batch(plan, 0, seqs)).float().unsqueeze(1)
-    assert torch.equal(shard.gather_embeddings(local, plan)[:, 0], torch.arange(12).float())
+    assert torch.equal(shard.gather_embeddings(local, plan, restore=True)[:, 0], torch.arange(12).float())
     pooled = torch.tensor([[0.0], [4.0], [6.0]])                       # one row per sequence, callers' order
     local_rows = pooled[torch.from_numpy(np.asarray(plan.groups[0]))]   # as rank 0 produces them
     assert torch.equal(shard.gather_pooled(local_rows, plan), pooled)
