@@ -813,8 +813,15 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the other seeded workloads (cfg1, cfg2 with and without graphs, cfg4, cfg5)")
+    ap.add_argument("--gemm-pair", type=int, choices=(0, 1), default=None,
+                    help="A/B switch: 0 runs every GEMM on single-CTA 128 x 256 tiles instead of CTA pairs")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
+    if args.gemm_pair is not None and args.impl == "ours":
+        load_package()
+        from flash_modernbert_b200 import _lib
+
+        _lib.check(_lib.load().pe_set_option(_lib.OPT_GEMM_PAIR, args.gemm_pair), "pe_set_option")
     run_arm(args, args.impl)
 
 

@@ -30,6 +30,7 @@ _ERR_NAMES = {
 }
 OPT_FUSED_GEGLU = 1
 OPT_FUSED_ROPE = 2
+OPT_GEMM_PAIR = 3
 OPT_FUSED_RESIDUAL = 4
 
 

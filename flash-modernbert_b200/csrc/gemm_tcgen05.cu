@@ -2,45 +2,74 @@
 // written for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with the
 // fp32 accumulator in tensor memory, persistent CTAs.
 //
-// One CTA per SM walks output tiles of 128 rows x 256 accumulator columns.
-//   warp 0      : TMA producer (one elected lane) - A box 128x64, two W boxes 128x64
-//   warp 1      : allocates tensor memory, issues tcgen05.mma (one elected lane)
-//   warps 2..5  : epilogue - tcgen05.ld the accumulator, round to bf16, store
+// Two forms of one kernel template.
+// PAIR (the default for all but tiny M): the two CTAs of a cluster of 2 share output tiles of
+// 256 rows x 256 accumulator columns (tcgen05 cta_group::2).  Each CTA stages its own 128 rows of
+// A and its own 128 rows of W per k block (32 KB instead of 48 KB per 128 x 256 x 64 block of
+// work), owns 128 lanes x 256 columns of the accumulator in its tensor memory and runs the
+// epilogue for its own 128 rows; one thread of the even CTA issues the MMAs for both.  Every CTA
+// fetches its own operands with plain per-CTA TMA loads; the two CTAs meet only in mbarriers.
+// Single CTA (M <= 256, or pe_set_option(PE_OPT_GEMM_PAIR, 0)): one CTA per SM, 128 x 256 tiles.
+//   warp 0      : TMA producer (one elected lane)
+//   warp 1      : allocates tensor memory, issues tcgen05.mma (one elected lane; in a pair only
+//                 the even CTA's)
+//   warps 2..5  : epilogue - tcgen05.ld the accumulator, round to bf16, transform, store
 // Tensor memory holds two 256-column accumulators, so the epilogue of tile i
 // overlaps the main loop of tile i+1.  The k loop runs over 64-wide blocks through
-// a 4-stage ring of (A 16 KB + W 32 KB) buffers guarded by full/empty mbarriers.
+// a ring of stage buffers guarded by full/empty mbarriers.
 //
 // GEGLU mode computes the first half of the MLP in one pass: the 256 accumulator
 // columns of a tile are 128 columns of the gelu input (rows n0.. of Wi) and the
-// matching 128 gate columns (rows I + n0.. of Wi); the epilogue rounds both to
-// bf16, as the unfused path materialises them, and writes gelu(a) * gate.
+// matching 128 gate columns (rows I + n0.. of Wi; in a pair, the odd CTA's half of B); the
+// epilogue rounds both to bf16, as the unfused path materialises them, and writes gelu(a) * gate.
+//
+// RESIDUAL mode in a pair streams the residual tile X through shared memory: each epilogue warp
+// keeps four 32-row x 64-column buffers; its elected lane TMA-loads X blocks two ahead of use,
+// every lane adds its accumulator row to its row of the block in place (swizzled, conflict free)
+// and the same buffer is handed to a TMA store.  No global load latency and no transposition is
+// left in the epilogue warps.
 //
 // Every mbarrier wait is bounded; a wait that gives up records a code in the
 // status word and the CTA unwinds through the common exit, which frees its
 // tensor memory.
+#include <algorithm>
+#include <atomic>
+
 #include "pe_host.h"
 #include "pe_ptx.cuh"
 
 namespace pe {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int BM = 128;   // rows per CTA
+constexpr int BN = 256;   // accumulator columns per tile
 constexpr int BK = 64;
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GEMM_THREADS = 192;
 constexpr int OUT_STAGE_BYTES = 32 * 128;  // one warp's 32 rows x 64 bf16 columns
-constexpr int OUT_BYTES = 4 * 2 * OUT_STAGE_BYTES;  // four epilogue warps, double-buffered
-constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + OUT_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t TMEM_COLS = 512;
+constexpr int X_LOOKAHEAD = 2;  // residual blocks in flight ahead of the one being added
+
+enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2, GEMM_RESIDUAL = 3, GEMM_L2NORM = 4 };
+
+template <int MODE, bool PAIR>
+struct GemmCfg {
+  static constexpr bool XTMA = PAIR && MODE == GEMM_RESIDUAL;  // residual blocks arrive by TMA
+  static constexpr int B_ROWS = PAIR ? 128 : 256;              // rows of W one CTA stages per k block
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = PAIR ? (XTMA ? 5 : 6) : 4;
+  static constexpr int OUT_BUFS = XTMA ? 4 : 2;                // staging buffers per epilogue warp
+  static constexpr int OUT_BYTES = 4 * OUT_BUFS * OUT_STAGE_BYTES;
+  // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2],
+  // x_full[4 warps][4 buffers]; then the tensor-memory base address
+  static constexpr int BAR_FULL = 0, BAR_EMPTY = STAGES, BAR_TFULL = 2 * STAGES, BAR_TEMPTY = 2 * STAGES + 2,
+                       BAR_XFULL = 2 * STAGES + 4, BAR_COUNT = 2 * STAGES + 4 + 16;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + OUT_BYTES + 1024 /*align*/ + 8 * BAR_COUNT + 16;
+};
 
 __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
-
-enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2, GEMM_RESIDUAL = 3, GEMM_L2NORM = 4 };
 
 // Extra operands of the Wqkv + RoPE epilogue and of the residual epilogue.
 struct RopeArgs {
@@ -51,45 +80,60 @@ struct RopeArgs {
   int max_positions;
 };
 
-template <int MODE>
+template <int MODE, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmC, int M, int n_out, int K, int gate_row0,
-                    int num_m, int num_n, RopeArgs rope, int* status) {
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
+                    int M, int n_out, int K, int gate_row0, int num_m, int num_n, RopeArgs rope,
+                    int* status) {
+  using Cfg = GemmCfg<MODE, PAIR>;
   constexpr bool GEGLU = MODE == GEMM_GEGLU;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t out_base = base + STAGES * STAGE_BYTES;
-  const uint32_t bar_base = out_base + OUT_BYTES;
-  // barrier slots (8 bytes each): full[0..3], empty[4..7], tmem_full[8..9], tmem_empty[10..11]
+  const uint32_t bar_base = out_base + Cfg::OUT_BYTES;
   auto bar = [&](int i) { return bar_base + 8u * i; };
-  const uint32_t tmem_slot = bar_base + 8u * 12;
+  const uint32_t tmem_slot = bar_base + 8u * Cfg::BAR_COUNT;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (K + BK - 1) / BK;
   const int num_tiles = num_m * num_n;
+  // In a pair both CTAs walk the same tiles; the odd CTA owns rows 128..255 of each.
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const int first_tile = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x);
+  const int tile_stride = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
+  constexpr int TILE_ROWS = PAIR ? 2 * BM : BM;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
-      mbar_init(bar(i), 1);
-      mbar_init(bar(4 + i), 1);
+      mbar_init(bar(Cfg::BAR_FULL + i), 1);
+      mbar_init(bar(Cfg::BAR_EMPTY + i), 1);
     }
-    mbar_init(bar(8), 1);
-    mbar_init(bar(9), 1);
-    mbar_init(bar(10), 4);
-    mbar_init(bar(11), 4);
+    mbar_init(bar(Cfg::BAR_TFULL), 1);
+    mbar_init(bar(Cfg::BAR_TFULL + 1), 1);
+    mbar_init(bar(Cfg::BAR_TEMPTY), PAIR ? 8 : 4);  // one arrival per epilogue warp (of both CTAs)
+    mbar_init(bar(Cfg::BAR_TEMPTY + 1), PAIR ? 8 : 4);
+    for (int i = 0; i < 16; ++i) mbar_init(bar(Cfg::BAR_XFULL + i), 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmC);
+    if (Cfg::XTMA) tma_prefetch_desc(&tmX);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all(); else __syncthreads();  // the peer's barriers are initialised too
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
@@ -98,22 +142,35 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / num_n) * BM;
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
+        const int m0 = (tile / num_n) * TILE_ROWS + int(cta_rank) * BM;
         const int nt = tile % num_n;
-        const int brow0 = GEGLU ? nt * 128 : nt * BN;
-        const int brow1 = GEGLU ? gate_row0 + nt * 128 : nt * BN + 128;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(bar(4 + stage), phase ^ 1u, status, ST_GEMM_PRODUCER_TIMEOUT)) {
+          if (!mbar_wait(bar(Cfg::BAR_EMPTY + stage), phase ^ 1u, status, ST_GEMM_PRODUCER_TIMEOUT)) {
             ok = false;
             break;
           }
           const uint32_t sa = base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
-          mbar_expect_tx(bar(stage), STAGE_BYTES);
-          tma_load_2d(sa, &tmA, bar(stage), kb * BK, m0);
-          tma_load_2d(sb, &tmB, bar(stage), kb * BK, brow0);
-          tma_load_2d(sb + B_BYTES / 2, &tmB, bar(stage), kb * BK, brow1);
+          if (PAIR) {
+            // Both CTAs' bytes are counted on the leader's barrier: its MMA thread waits for the
+            // whole 256-row stage.  The odd CTA's half of B: rows 128..255 of the tile's 256 W rows,
+            // or the gate rows in GEGLU mode.
+            const uint32_t full = cta_rank == 0 ? bar(Cfg::BAR_FULL + stage)
+                                                : cluster_map(bar(Cfg::BAR_FULL + stage), 0);
+            const int brow = GEGLU ? (cta_rank == 0 ? nt * 128 : gate_row0 + nt * 128)
+                                   : nt * BN + int(cta_rank) * 128;
+            if (cta_rank == 0) mbar_expect_tx(full, 2 * STAGE_BYTES);
+            tma_load_2d_pair(sa, &tmA, full, kb * BK, m0);
+            tma_load_2d_pair(sb, &tmB, full, kb * BK, brow);
+          } else {
+            const int brow0 = GEGLU ? nt * 128 : nt * BN;
+            const int brow1 = GEGLU ? gate_row0 + nt * 128 : nt * BN + 128;
+            mbar_expect_tx(bar(Cfg::BAR_FULL + stage), STAGE_BYTES);
+            tma_load_2d(sa, &tmA, bar(Cfg::BAR_FULL + stage), kb * BK, m0);
+            tma_load_2d(sb, &tmB, bar(Cfg::BAR_FULL + stage), kb * BK, brow0);
+            tma_load_2d(sb + Cfg::B_BYTES / 2, &tmB, bar(Cfg::BAR_FULL + stage), kb * BK, brow1);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -123,16 +180,16 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0);
+    if (cta_rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(TILE_ROWS, BN, 0);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(bar(10 + acc), acc_phase ^ 1u, status, ST_GEMM_MMA_TIMEOUT)) break;
+      for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
+        if (!mbar_wait(bar(Cfg::BAR_TEMPTY + acc), acc_phase ^ 1u, status, ST_GEMM_MMA_TIMEOUT)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(bar(stage), phase, status, ST_GEMM_MMA_TIMEOUT)) {
+          if (!mbar_wait(bar(Cfg::BAR_FULL + stage), phase, status, ST_GEMM_MMA_TIMEOUT)) {
             ok = false;
             break;
           }
@@ -143,16 +200,19 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
             // 16 bf16 along K = 32 bytes = 2 descriptor address units inside the swizzle atom
-            umma_ss(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+            if (PAIR) umma_ss_pair(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+            else umma_ss(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
-          umma_commit(bar(4 + stage));
+          if (PAIR) umma_commit_pair(bar(Cfg::BAR_EMPTY + stage));  // frees the stage in both CTAs
+          else umma_commit(bar(Cfg::BAR_EMPTY + stage));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit(bar(8 + acc));
+        if (PAIR) umma_commit_pair(bar(Cfg::BAR_TFULL + acc));
+        else umma_commit(bar(Cfg::BAR_TFULL + acc));
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -165,7 +225,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // per instruction; the TMA store keeps the load/store unit out of the way and clips rows
     // and columns that fall outside C.
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
-    const uint32_t stage0 = out_base + q * 2 * OUT_STAGE_BYTES;
+    const uint32_t stage0 = out_base + q * Cfg::OUT_BUFS * OUT_STAGE_BYTES;
     uint32_t ob = 0;  // staging buffer in use
     auto emit64 = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int col, int row0) {
       if (lane == 0) tma_store_wait_read<1>();  // the buffer used two stores ago is free again
@@ -210,11 +270,35 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     };
     const bool res_chain = (MODE == GEMM_RESIDUAL) && (n_out % BN == 0);
     bool res_ready = false;
+    // XTMA: this warp's stream of residual blocks (32 rows x 64 columns each), numbered across
+    // tiles; block n lives in buffer n & 3 and completes phase (n >> 2) & 1 of that buffer's
+    // barrier.  The elected lane keeps X_LOOKAHEAD blocks in flight.
+    uint32_t xn = 0;            // blocks consumed so far
+    int xl_tile = first_tile;   // next block to load: tile and 64-column chunk
+    int xl_c = 0;
+    uint32_t xl_n = 0;          // blocks loaded so far
+    auto x_load_next = [&]() {  // lane 0 only
+      if (xl_tile >= num_tiles) return;
+      const int xm0 = (xl_tile / num_n) * TILE_ROWS + int(cta_rank) * BM + q * 32;
+      const int xcol = (xl_tile % num_n) * BN + xl_c * 64;
+      const uint32_t b = xl_n & 3u;
+      mbar_expect_tx(bar(Cfg::BAR_XFULL + q * 4 + b), OUT_STAGE_BYTES);
+      tma_load_2d(stage0 + b * OUT_STAGE_BYTES, &tmX, bar(Cfg::BAR_XFULL + q * 4 + b), xcol, xm0);
+      ++xl_n;
+      if (++xl_c == BN / 64 || (xl_tile % num_n) * BN + xl_c * 64 >= n_out) {
+        xl_c = 0;
+        xl_tile += tile_stride;
+      }
+    };
+    if (Cfg::XTMA && lane == 0) {
+#pragma unroll 1
+      for (int i = 0; i < X_LOOKAHEAD; ++i) x_load_next();
+    }
     uint32_t acc = 0, acc_phase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile / num_n) * BM;
+    for (int tile = first_tile; tile < num_tiles; tile += tile_stride) {
+      const int m0 = (tile / num_n) * TILE_ROWS + int(cta_rank) * BM;
       const int nt = tile % num_n;
-      if (!mbar_wait(bar(8 + acc), acc_phase, status, ST_GEMM_EPILOGUE_TIMEOUT)) break;
+      if (!mbar_wait(bar(Cfg::BAR_TFULL + acc), acc_phase, status, ST_GEMM_EPILOGUE_TIMEOUT)) break;
       tc_fence_after();
       const int row0 = m0 + q * 32;
       const int row = row0 + lane;
@@ -255,6 +339,59 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           emit64(lo, hi, col, row0);
         }
+      } else if constexpr (Cfg::XTMA) {
+        // C = bf16(X + bf16(acc)), X streamed through this warp's four staging buffers by TMA.
+        // Lane l owns row l of the block: eight 16-byte chunks at the swizzled offsets a TMA box
+        // uses, so loads and stores are conflict free and the sum is stored from the same buffer.
+        // X may be C: block n is loaded before block n is stored, and no other block overlaps it.
+        const int col0 = nt * BN;
+        bool x_ok = true;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col = col0 + c * 64;
+          if (col >= n_out) break;
+          const uint32_t b = xn & 3u;
+          const uint32_t buf = stage0 + b * OUT_STAGE_BYTES;
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32(t_addr + c * 64, lo);
+          tmem_ld_32x32(t_addr + c * 64 + 32, hi);
+          if (x_ok && !mbar_wait(bar(Cfg::BAR_XFULL + q * 4 + b), (xn >> 2) & 1u, status, ST_GEMM_EPILOGUE_TIMEOUT))
+            x_ok = false;
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t addr = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
+            uint4 xv;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(xv.x), "=r"(xv.y), "=r"(xv.z), "=r"(xv.w)
+                         : "r"(addr));
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 xf = __bfloat1622float2(xp[e]);
+              const uint32_t* src = j < 4 ? lo : hi;
+              const float a0 = round_bf16(__uint_as_float(src[(j & 3) * 8 + 2 * e]));
+              const float a1 = round_bf16(__uint_as_float(src[(j & 3) * 8 + 2 * e + 1]));
+              o[e] = pack_bf16(xf.x + a0, xf.y + a1);
+            }
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]),
+                         "r"(o[2]), "r"(o[3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          ++xn;
+          if (lane == 0) {
+            if (x_ok) tma_store_2d(&tmC, buf, col, row0);
+            tma_store_commit();
+            // Block xn + 1 goes into the buffer that held block xn - 3, whose store is two
+            // commits back: wait until at most the two newest stores still read their buffers.
+            tma_store_wait_read<2>();
+            if (x_ok) x_load_next();
+          }
+        }
+        if (!x_ok) break;
       } else if constexpr (MODE == GEMM_RESIDUAL) {
         // C = bf16(X + bf16(acc)).  The warp fetches its 32 x 64 block of X coalesced (four rows
         // per instruction), one block ahead of the accumulator it belongs to, turns it into
@@ -401,7 +538,10 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(10 + acc));
+      if (lane == 0) {  // the accumulator is free again: tell the (leader's) MMA thread
+        if (cta_rank == 0) mbar_arrive(bar(Cfg::BAR_TEMPTY + acc));
+        else mbar_arrive_cluster(cluster_map(bar(Cfg::BAR_TEMPTY + acc), 0));
+      }
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -409,22 +549,28 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __syncwarp();
   }
 
-  // Common exit: every role arrives here (each of its waits is bounded).
+  // Common exit: every role arrives here (each of its waits is bounded).  In a pair both CTAs
+  // must be done before either frees tensor memory that the leader's MMAs write.
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all(); else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
-template <int MODE>
-static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_out, int K,
-                       int w_rows, int gate_row0, RopeArgs rope, int32_t* status,
-                       cudaStream_t stream) {
+static std::atomic<int> g_gemm_pair{1};
+void set_gemm_pair(int on) { g_gemm_pair.store(on, std::memory_order_relaxed); }
+
+template <int MODE, bool PAIR>
+static int launch_gemm_as(const void* A, const void* W, void* C, int64_t M, int n_out, int K,
+                          int w_rows, int gate_row0, RopeArgs rope, int32_t* status,
+                          cudaStream_t stream) {
+  using Cfg = GemmCfg<MODE, PAIR>;
   constexpr bool GEGLU = MODE == GEMM_GEGLU;
-  auto kern = gemm_bf16_tn_kernel<MODE>;
-  int rc = set_max_dynamic_smem(reinterpret_cast<const void*>(kern), GEMM_SMEM, false);
+  auto kern = gemm_bf16_tn_kernel<MODE, PAIR>;
+  int rc = set_max_dynamic_smem(reinterpret_cast<const void*>(kern), Cfg::SMEM, false);
   if (rc != PE_OK) return rc;
   CUtensorMap tmA, tmB;
   rc = make_tmap_bf16_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM);
@@ -434,16 +580,49 @@ static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_o
   CUtensorMap tmC;  // output, stored in 32-row x 64-column boxes
   rc = make_tmap_bf16_2d(&tmC, C, (uint64_t)M, (uint64_t)n_out, (uint64_t)n_out, 32);
   if (rc != PE_OK) return rc;
-  const int num_m = int((M + BM - 1) / BM);
+  CUtensorMap tmX = tmC;  // residual, loaded in the same boxes (RESIDUAL mode in a pair)
+  if (Cfg::XTMA) {
+    rc = make_tmap_bf16_2d(&tmX, rope.residual, (uint64_t)M, (uint64_t)n_out, (uint64_t)n_out, 32);
+    if (rc != PE_OK) return rc;
+  }
+  const int tile_rows = PAIR ? 2 * BM : BM;
+  const int num_m = int((M + tile_rows - 1) / tile_rows);
   const int cols_per_tile = GEGLU ? 128 : BN;
   const int num_n = (n_out + cols_per_tile - 1) / cols_per_tile;
   const long long tiles = (long long)num_m * num_n;
-  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, tmC,
-                                                  (int)M, n_out, K, gate_row0, num_m, num_n,
-                                                  rope, status);
+  if (PAIR) {
+    const long long pairs = std::min<long long>(tiles, sm_count() / 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PE_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmX, (int)M, n_out, K, gate_row0, num_m, num_n,
+                               rope, (int*)status));
+  } else {
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(tmA, tmB, tmC, tmX, (int)M, n_out, K, gate_row0,
+                                                    num_m, num_n, rope, status);
+  }
   PE_LAUNCH_CHECK("gemm_bf16_tn_kernel");
   return PE_OK;
+}
+
+template <int MODE>
+static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_out, int K,
+                       int w_rows, int gate_row0, RopeArgs rope, int32_t* status,
+                       cudaStream_t stream) {
+  // A pair needs more than one CTA's worth of rows to be worth its second CTA.
+  if (M > 2 * BM && g_gemm_pair.load(std::memory_order_relaxed) != 0)
+    return launch_gemm_as<MODE, true>(A, W, C, M, n_out, K, w_rows, gate_row0, rope, status, stream);
+  return launch_gemm_as<MODE, false>(A, W, C, M, n_out, K, w_rows, gate_row0, rope, status, stream);
 }
 
 static int check_gemm_args(const void* A, const void* W, const void* C, int64_t M, int n, int K,

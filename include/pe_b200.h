@@ -91,6 +91,9 @@ int pe_device_check(void);
 /* key 2 (PE_OPT_FUSED_ROPE, default 1): Wqkv and RoPE as one kernel (1) or as pe_gemm_bf16_tn
  * followed by pe_rope_qk_inplace (0). */
 #define PE_OPT_FUSED_ROPE 2
+/* key 3 (PE_OPT_GEMM_PAIR, default 1): every GEMM with more than 256 rows runs on pairs of CTAs
+ * sharing 256 x 256 tiles (1), or on single CTAs with 128 x 256 tiles (0).  Same results. */
+#define PE_OPT_GEMM_PAIR 3
 /* key 4 (PE_OPT_FUSED_RESIDUAL, default 1): Wo and the MLP's Wo add their result to the residual
  * stream in the GEMM epilogue and the norms run as plain LayerNorms (1), or the projections are
  * materialised and pe_add_ln adds them (0). */

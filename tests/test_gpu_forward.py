@@ -444,6 +444,20 @@ def test_graphs_precaptured_at_pack_time(pe, cuda_device, tiny_models):
         pe.unpack(gpu)
 
 
+def _same_up_to_p_rounding(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Sequences longer than 64 tokens go through the tensor-memory attention kernels, whose
+    sliding-window form may take its softmax reference exponent from a whole fetched key chunk,
+    rows beyond the end of the sequence included (any reference within 2^60 of the row maximum
+    serves). A graph bucket holds padding rows there where the eager batch holds nothing, so P
+    can round differently by one bf16 step at the ends of sequences: equal to within that, not
+    bit for bit."""
+    worst, max_abs = _token_cosines(a.reshape(-1, a.shape[-1]), b.reshape(-1, b.shape[-1]))
+    live = (a.float().abs().amax(dim=-1) > 0).reshape(-1)
+    x, y = a.reshape(-1, a.shape[-1])[live].float(), b.reshape(-1, b.shape[-1])[live].float()
+    cos = (x * y).sum(-1) / (x.norm(dim=-1) * y.norm(dim=-1)).clamp_min(1e-12)
+    return float(cos.min()) > 0.9999 and max_abs < 0.05 and torch.equal(a == 0, b == 0)
+
+
 def _padded(seqs, b_cols=None):
     b, s = len(seqs), b_cols or max(x.numel() for x in seqs)
     ids = torch.zeros(b, s, dtype=torch.int64)
@@ -488,10 +502,10 @@ def test_padded_api_through_cuda_graphs(pe, cuda_device, tiny_models):
         assert runner.captures == 1 and runner.replays == 3
         ids, mask = batch(4, 70, 128)                         # the 128 bucket: tensor-memory attention
         graphed, eager = both(ids, mask)
-        assert torch.equal(graphed, eager) and runner.captures == 2
+        assert _same_up_to_p_rounding(graphed, eager) and runner.captures == 2
         ids, mask = batch(2, 130, 190)                        # a third bucket evicts the oldest
         graphed, eager = both(ids, mask)
-        assert torch.equal(graphed, eager)
+        assert _same_up_to_p_rounding(graphed, eager)
         assert runner.captures == 3 and list(runner._cache) == [(8, 128), (8, 192)]
         before = runner.eager_calls
         ids, mask = batch(2, 201, 260)                        # over max_seq: eager
@@ -563,7 +577,8 @@ def test_non_finite_bucket_padding_never_reaches_real_rows(pe, cuda_device, tiny
                 eager = pe.packed_forward(gpu, params, *batch.forward_args())
         assert runner.replays == 2
         assert bool(torch.isfinite(poisoned.float()).all())
-        assert torch.equal(poisoned, eager) and torch.equal(first, eager)
+        assert torch.equal(poisoned, first)                      # what the padding held before does not matter
+        assert _same_up_to_p_rounding(poisoned, eager)
     finally:
         pe.unpack(gpu)
 

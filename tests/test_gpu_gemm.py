@@ -126,3 +126,34 @@ def test_inplace_residual_with_several_tiles_per_cta(pe, cuda_device, m, n, k):
     ops.check_status(cuda_device)
     assert torch.equal(inplace, expected)
     assert torch.equal(ops.linear_residual(a_d, w_d, res), expected)
+
+
+@pytest.mark.parametrize("m", [257, 1000, 4097])
+def test_cta_pair_and_single_cta_tiles_agree(pe, cuda_device, m):
+    """Above 256 rows every GEMM runs on pairs of CTAs sharing 256 x 256 tiles (cta_group::2);
+    `pe_set_option(PE_OPT_GEMM_PAIR, 0)` selects the single-CTA 128 x 256 tiles. Same k order and
+    the same epilogues: identical bits in every mode, including ragged last tiles."""
+    from flash_modernbert_b200 import _lib, ops
+
+    lib = _lib.load()
+    a, w, a_d, w_d = _inputs(m, 2304, 768, cuda_device, seed=21)
+    _, wo, _, wo_d = _inputs(m, 768, 768, cuda_device, seed=22)
+    _, wp, _, wp_d = _inputs(m, 128, 768, cuda_device, seed=23)
+    res = torch.randn(m, 768, generator=torch.Generator().manual_seed(24)).to(torch.bfloat16).to(cuda_device)
+    pos = torch.randint(0, 512, (m,), generator=torch.Generator().manual_seed(m)).to(cuda_device)
+    table = ops.rope_table(160000.0, 512, cuda_device)
+
+    def run_all():
+        return [ops._linear(a_d, w_d), ops.linear_geglu(a_d, w_d), ops.linear_qkv_rope(a_d, w_d, pos, table, 12),
+                ops.linear_residual(a_d, wo_d, res), ops.linear_residual(a_d, wo_d, res.clone(), inplace=True),
+                ops.project_normalize(a_d, wp_d)]
+
+    paired = run_all()
+    try:
+        assert lib.pe_set_option(_lib.OPT_GEMM_PAIR, 0) == 0
+        single = run_all()
+    finally:
+        lib.pe_set_option(_lib.OPT_GEMM_PAIR, 1)
+    ops.check_status(cuda_device)
+    for name, x, y in zip(("plain", "geglu", "rope", "residual", "residual in place", "l2norm"), paired, single):
+        assert torch.equal(x, y), name
