@@ -424,10 +424,9 @@ int attn_schedule(const int32_t* cu_seqlens, int n_seqs, int64_t T, int bm, bool
 }
 
 static int launch_short(const __nv_bfloat16* q, const int4* info, const int32_t* total, int64_t max_tiles,
-                        int bm, int nh, int half_window, __nv_bfloat16* o, cudaStream_t st) {
-  // four heads per CTA (see the kernel): enough CTAs to fill the GPU, few enough that each hides
-  // its own load latency
-  dim3 grid((unsigned)max_tiles, (unsigned)((nh + 3) / 4));
+                        int bm, int nh, int half_window, int heads_per_cta, __nv_bfloat16* o,
+                        cudaStream_t st) {
+  dim3 grid((unsigned)max_tiles, (unsigned)((nh + heads_per_cta - 1) / heads_per_cta));
   switch (bm) {
     case 16:
       attn_varlen_mma_kernel<1><<<grid, 32, 0, st>>>(q, info, total, nh, half_window, o);
@@ -451,7 +450,9 @@ int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh
   const TileTables t = tile_tables(const_cast<void*>(scratch), n_seqs, T, bm);
   const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(qkv);
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
-  if (bm != 128) return launch_short(q, t.tile_info, t.tile_start + n_seqs, t.cap_long, bm, nh, half_window, o, st);
+  // A batch of short sequences only: four heads per CTA (see the kernel) - enough CTAs to fill the
+  // GPU, few enough that each hides its own load latency.
+  if (bm != 128) return launch_short(q, t.tile_info, t.tile_start + n_seqs, t.cap_long, bm, nh, half_window, 4, o, st);
   // Long batch: the tensor-memory kernels take the sequences of more than 64 tokens (at most
   // T / 128 + T / 65 tiles of them exist), the register kernel with 64-row tiles the rest.
   const int64_t max_long = std::min<int64_t>(t.cap_long, T / 128 + T / (ATT_SHORT_MAX + 1) + 1);
@@ -460,8 +461,10 @@ int attn_run(const void* qkv, const void* scratch, int n_seqs, int64_t T, int nh
                : attn_run_global_tc(qkv, t.tile_info, t.tile_start + n_seqs, max_long, T, nh, half_window,
                                     out, status, st);
   if (rc != PE_OK) return rc;
+  // Usually few sequences are short here, so this launch is a latency chain, not a throughput
+  // problem: one head per CTA keeps the chain at a quarter of the four-head form's.
   const int64_t max_short = std::min<int64_t>(n_seqs, T);
-  return launch_short(q, t.short_info, t.short_start + n_seqs, max_short, 64, nh, half_window, o, st);
+  return launch_short(q, t.short_info, t.short_start + n_seqs, max_short, 64, nh, half_window, 1, o, st);
 }
 
 // ---- scratch that needs no allocation -------------------------------------------------

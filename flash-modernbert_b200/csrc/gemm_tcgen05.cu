@@ -619,8 +619,11 @@ template <int MODE>
 static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_out, int K,
                        int w_rows, int gate_row0, RopeArgs rope, int32_t* status,
                        cudaStream_t stream) {
-  // A pair needs more than one CTA's worth of rows to be worth its second CTA.
-  if (M > 2 * BM && g_gemm_pair.load(std::memory_order_relaxed) != 0)
+  // A pair needs more than one CTA's worth of rows to be worth its second CTA.  The GEGLU
+  // epilogue (a GELU per output element) takes about as long as a tile's main loop; coupled to
+  // its peer's, as the shared accumulator hand-over couples them, it runs 11 % slower than on
+  // independent CTAs (204.6 against 184.7 us at 71,567 rows), so that mode stays on single CTAs.
+  if (MODE != GEMM_GEGLU && M > 2 * BM && g_gemm_pair.load(std::memory_order_relaxed) != 0)
     return launch_gemm_as<MODE, true>(A, W, C, M, n_out, K, w_rows, gate_row0, rope, status, stream);
   return launch_gemm_as<MODE, false>(A, W, C, M, n_out, K, w_rows, gate_row0, rope, status, stream);
 }

@@ -53,3 +53,40 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row(pe, cuda_device):
     rc = lib.pe_attn_varlen_static(qkv.data_ptr(), cu.data_ptr(), 1, (1 << 20) + 1, 1, -1, 16,
                                    out.data_ptr(), None, _lib.current_stream_ptr())
     assert rc == _lib.PE_ERR_WORKSPACE
+
+
+def test_static_scratch_allocates_nothing_and_works_at_its_limits(pe, cuda_device):
+    """At exactly the documented maximum (4,096 sequences, 1,048,576 tokens) the built-in table
+    is large enough and the result equals the caller-scratch entry point's; one token or one
+    sequence more is refused. Around direct calls through the C ABI the device's free memory and
+    torch's allocation count do not move: the entry point reserves nothing."""
+    from flash_modernbert_b200 import _lib, ops
+
+    lib = _lib.load()
+    lengths = [256] * 4096
+    total = sum(lengths)
+    assert total == 1 << 20
+    qkv, cu = _case(lengths, 1, 31, cuda_device)
+    out = torch.empty(total, 64, dtype=torch.bfloat16, device=cuda_device)
+    status = ops.status_word(cuda_device)
+    stream = _lib.current_stream_ptr()
+
+    def call(n_seqs, tokens):
+        return lib.pe_attn_varlen_static(qkv.data_ptr(), cu.data_ptr(), n_seqs, tokens, 1, 64, 256,
+                                         out.data_ptr(), status.data_ptr(), stream)
+
+    assert call(4096, total) == 0, _lib.last_error()          # first call: looks the array's address up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(cuda_device)
+    allocated_before = torch.cuda.memory_allocated(cuda_device)
+    out.zero_()
+    assert call(4096, total) == 0 and call(4096, total) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(cuda_device)
+    assert torch.cuda.memory_allocated(cuda_device) == allocated_before
+    assert free_after == free_before
+    ops.check_status(cuda_device)
+    expected = ops.attention_varlen_qkv(qkv, cu, 256, 1, 64)
+    assert torch.equal(out, expected)
+    assert call(4097, total) == _lib.PE_ERR_WORKSPACE
+    assert call(4096, total + 1) == _lib.PE_ERR_WORKSPACE
