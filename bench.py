@@ -212,9 +212,12 @@ def launches_per_forward(model, max_seqlen: int, pooled: bool = False) -> int:
     return n + (3 if pooled else 1)  # final LN, or pool schedule + fused LN/pool + finish
 
 
-def time_gemm_kernels(model, tokens: int, device, clocks: "ClockSampler | None" = None, reps: int = 40) -> dict:
-    """Average duration of each GEMM launch shape of one layer, timed alone with CUDA
-    events on the launching stream (each launch streams > 126 MB, so L2 does not hold it)."""
+def time_gemm_kernels(model, tokens: int, device, clocks: "ClockSampler | None" = None,
+                      bursts: int = 6, burst_len: int = 8, sustained_reps: int = 40) -> dict:
+    """Duration of each GEMM launch shape of one layer, timed alone with CUDA events on the
+    launching stream (each launch streams > 126 MB, so L2 does not hold it), two ways: the best of
+    several short bursts after a pause (how the burst peak it is compared with was measured: best
+    of 10), and the average of a long back-to-back run under the power cap (the sustained figure)."""
     load_package()
     from flash_modernbert_b200 import ops
 
@@ -237,11 +240,8 @@ def time_gemm_kernels(model, tokens: int, device, clocks: "ClockSampler | None" 
         "Wo_mlp+residual": (lambda: ops.linear_residual(xi, layer.mlp.Wo.weight, xres, inplace=True),
                             2.0 * tokens * I * H),
     }
-    out = {}
-    for name, (fn, flops) in shapes.items():
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize(device)
+
+    def timed(fn, reps):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         start.record()
@@ -249,11 +249,23 @@ def time_gemm_kernels(model, tokens: int, device, clocks: "ClockSampler | None" 
             fn()
         end.record()
         torch.cuda.synchronize(device)
-        t1 = time.perf_counter()
-        ms = start.elapsed_time(end) / reps
+        return start.elapsed_time(end) / reps, t0, time.perf_counter()
+
+    out = {}
+    for name, (fn, flops) in shapes.items():
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(device)
+        best = None
+        for _ in range(bursts):
+            time.sleep(0.03)
+            ms, _, _ = timed(fn, burst_len)
+            best = ms if best is None else min(best, ms)
+        ms_sus, t0, t1 = timed(fn, sustained_reps)
         mhz = clocks.median_between(t0, t1) if clocks is not None else None
-        out[name] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "flops": flops,
-                     "sm_mhz": mhz, "kcycles": round(ms * mhz, 1) if mhz else None}
+        out[name] = {"ms": round(best, 4), "tflops": round(flops / best / 1e9, 1), "flops": flops,
+                     "ms_sustained": round(ms_sus, 4), "tflops_sustained": round(flops / ms_sus / 1e9, 1),
+                     "sm_mhz_sustained": mhz, "kcycles_sustained": round(ms_sus * mhz, 1) if mhz else None}
     return out
 
 
@@ -763,22 +775,25 @@ def run_arm(args, impl: str) -> None:
         gemm_ms_layer = sum(v["ms"] for v in gemm.values())
         gemm_flops_layer = sum(v["flops"] for v in gemm.values())
         achieved = gemm_flops_layer / gemm_ms_layer / 1e9
+        achieved_sustained = gemm_flops_layer / sum(v["ms_sustained"] for v in gemm.values()) / 1e9
         flops_ms = (work["gemm_flops"] + work["attn_flops"]) / (peaks["bf16_tflops_sustained"] * 1e9)
         ideal_ms = flops_ms + work["tail_bytes"] / (peaks["hbm_gbs"] * 1e6)
         ideal_fused_ms = flops_ms + work["tail_bytes_fused"] / (peaks["hbm_gbs"] * 1e6)
         line["roofline"] = {
             "bound": "tensor", "kernel": "gemm_bf16_tn_kernel (tcgen05; the four launches of one layer: Wqkv+RoPE, Wo+residual, Wi+GeGLU, Wo_mlp+residual)",
             "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-            "frac": round(achieved / peaks["bf16_tflops"], 4), "peak_source": f"{peaks['source']} burst",
-            "frac_of_sustained": round(achieved / peaks["bf16_tflops_sustained"], 4),
+            "frac": round(achieved / peaks["bf16_tflops"], 4),
+            "peak_source": f"{peaks['source']} burst (cuBLAS best of 10); achieved = best of 6 bursts of 8 launches per shape",
+            "sustained": {"achieved": round(achieved_sustained, 1), "peak": peaks["bf16_tflops_sustained"],
+                          "frac": round(achieved_sustained / peaks["bf16_tflops_sustained"], 4),
+                          "how": "40 launches back to back per shape, under the power cap, against the sustained cuBLAS peak"},
             "traffic": (round(NCU_GEMM_DRAM_BYTES_PER_TOKEN * batch.total_tokens / 1e9, 3)
                         if arch == "base" else None),
             "traffic_unit": "GB per layer (four launches)",
             "traffic_source": "not measured in this run: one ncu capture on a 71,567-token slice (activations partly "
                               "L2-resident there, so it reads low), scaled by tokens",
             "algorithmic_gb": round(19968 * batch.total_tokens / 1e9, 3),
-            "per_shape": {k: {"ms": v["ms"], "tflops": v["tflops"], "sm_mhz": v["sm_mhz"], "kcycles": v["kcycles"]}
-                          for k, v in gemm.items()},
+            "per_shape": {k: {kk: vv for kk, vv in v.items() if kk != "flops"} for k, v in gemm.items()},
         }
         line["step_model"] = {
             "gemm_tflop": round(work["gemm_flops"] / 1e12, 2), "attn_tflop": round(work["attn_flops"] / 1e12, 2),

@@ -620,10 +620,13 @@ static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_o
                        int w_rows, int gate_row0, RopeArgs rope, int32_t* status,
                        cudaStream_t stream) {
   // A pair needs more than one CTA's worth of rows to be worth its second CTA.  The GEGLU
-  // epilogue (a GELU per output element) takes about as long as a tile's main loop; coupled to
-  // its peer's, as the shared accumulator hand-over couples them, it runs 11 % slower than on
-  // independent CTAs (204.6 against 184.7 us at 71,567 rows), so that mode stays on single CTAs.
-  if (MODE != GEMM_GEGLU && M > 2 * BM && g_gemm_pair.load(std::memory_order_relaxed) != 0)
+  // epilogue (a GELU per output element) takes about as long as a 768-deep tile's main loop;
+  // coupled to its peer's, as the shared accumulator hand-over couples them, it then runs slower
+  // than on independent CTAs (0.856 against 0.823 ms at 306,851 x 2304 x 768), so that mode
+  // joins the pairs only from K = 1024 on, where the main loop hides it (1.98 against 2.04 ms at
+  // 262,144 x 5248 x 1024, 4.47 against 4.84 ms at 262,144 x 7680 x 1792).
+  const bool pair_pays = MODE != GEMM_GEGLU || K >= 1024;
+  if (pair_pays && M > 2 * BM && g_gemm_pair.load(std::memory_order_relaxed) != 0)
     return launch_gemm_as<MODE, true>(A, W, C, M, n_out, K, w_rows, gate_row0, rope, status, stream);
   return launch_gemm_as<MODE, false>(A, W, C, M, n_out, K, w_rows, gate_row0, rope, status, stream);
 }
