@@ -49,7 +49,10 @@ constexpr int OUT_STAGE_BYTES = 32 * 128;  // one warp's 32 rows x 64 bf16 colum
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int X_LOOKAHEAD = 2;  // residual blocks in flight ahead of the one being added
 
-enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2, GEMM_RESIDUAL = 3, GEMM_L2NORM = 4 };
+// GEMM_RESIDUAL_RED: the in-place form of GEMM_RESIDUAL (C is X): the plain epilogue, its TMA stores
+// replaced by TMA reduce-adds, so X is never read by the kernel at all.
+enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2, GEMM_RESIDUAL = 3, GEMM_L2NORM = 4,
+                      GEMM_RESIDUAL_RED = 5 };
 
 template <int MODE, bool PAIR>
 struct GemmCfg {
@@ -249,7 +252,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        tma_store_2d(&tmC, stage0 + ob * OUT_STAGE_BYTES, col, row0);
+        if constexpr (MODE == GEMM_RESIDUAL_RED) tma_reduce_add_2d(&tmC, stage0 + ob * OUT_STAGE_BYTES, col, row0);
+        else tma_store_2d(&tmC, stage0 + ob * OUT_STAGE_BYTES, col, row0);
         tma_store_commit();
       }
       ob ^= 1u;
@@ -562,6 +566,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 static std::atomic<int> g_gemm_pair{1};
 void set_gemm_pair(int on) { g_gemm_pair.store(on, std::memory_order_relaxed); }
+static std::atomic<int> g_residual_reduce{1};
+void set_residual_reduce(int on) { g_residual_reduce.store(on, std::memory_order_relaxed); }
 
 template <int MODE, bool PAIR>
 static int launch_gemm_as(const void* A, const void* W, void* C, int64_t M, int n_out, int K,
@@ -685,6 +691,11 @@ extern "C" int pe_gemm_residual_bf16(const void* A, const void* W, const void* X
   PE_REQUIRE(X != nullptr && ((uintptr_t)X & 15) == 0, "pe_gemm_residual_bf16: X is NULL or unaligned");
   pe::RopeArgs args{};
   args.residual = static_cast<const __nv_bfloat16*>(X);
+  // In place (the forward's case) nothing has to read X: the rounded product is ADDED to it by
+  // TMA reduce-adds, one bf16 add with one rounding per element, exactly the sum above.
+  if (X == C && pe::g_residual_reduce.load(std::memory_order_relaxed) != 0)
+    return pe::launch_gemm<pe::GEMM_RESIDUAL_RED>(A, W, C, M, Nout, K, Nout, 0, args, status,
+                                                  static_cast<cudaStream_t>(stream));
   return pe::launch_gemm<pe::GEMM_RESIDUAL>(A, W, C, M, Nout, K, Nout, 0, args, status,
                                             static_cast<cudaStream_t>(stream));
 }

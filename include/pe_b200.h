@@ -98,6 +98,10 @@ int pe_device_check(void);
  * stream in the GEMM epilogue and the norms run as plain LayerNorms (1), or the projections are
  * materialised and pe_add_ln adds them (0). */
 #define PE_OPT_FUSED_RESIDUAL 4
+/* key 5 (PE_OPT_RESIDUAL_REDUCE, default 1): pe_gemm_residual_bf16 called in place (C == X) adds
+ * its rounded product to X with TMA reduce-adds and never reads X (1), or loads X, adds and stores
+ * (0).  Same bits: one bf16 add with one rounding per element either way. */
+#define PE_OPT_RESIDUAL_REDUCE 5
 /* A forward reads the switches once, when it starts to enqueue its kernels. */
 int pe_set_option(int key, int value);
 

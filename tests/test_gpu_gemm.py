@@ -157,3 +157,25 @@ def test_cta_pair_and_single_cta_tiles_agree(pe, cuda_device, m):
     ops.check_status(cuda_device)
     for name, x, y in zip(("plain", "geglu", "rope", "residual", "residual in place", "l2norm"), paired, single):
         assert torch.equal(x, y), name
+
+
+@pytest.mark.parametrize("m,n,k", [(300, 768, 768), (4097, 768, 1152), (129, 1024, 2624), (513, 72, 200)])
+def test_inplace_residual_by_reduce_add_equals_load_add_store(pe, cuda_device, m, n, k):
+    """In place, the residual GEMM adds its rounded product to X with TMA reduce-adds (the memory
+    system performs the bf16 add) instead of reading X. One add with one rounding per element either
+    way: same bits as the form that loads X (`PE_OPT_RESIDUAL_REDUCE` = 0) and as the two-step form."""
+    from flash_modernbert_b200 import _lib, ops
+
+    lib = _lib.load()
+    a, w, a_d, w_d = _inputs(m, n, k, cuda_device, seed=31)
+    res = torch.randn(m, n, generator=torch.Generator().manual_seed(32)).to(torch.bfloat16).to(cuda_device)
+    expected = res + ops._linear(a_d, w_d)
+    by_reduce = ops.linear_residual(a_d, w_d, res.clone(), inplace=True)
+    try:
+        assert lib.pe_set_option(_lib.OPT_RESIDUAL_REDUCE, 0) == 0
+        by_load = ops.linear_residual(a_d, w_d, res.clone(), inplace=True)
+    finally:
+        lib.pe_set_option(_lib.OPT_RESIDUAL_REDUCE, 1)
+    ops.check_status(cuda_device)
+    assert torch.equal(by_load, expected)
+    assert torch.equal(by_reduce, expected)
