@@ -14,6 +14,9 @@
 //   warp 1      : allocates tensor memory, issues tcgen05.mma (one elected lane; in a pair only
 //                 the even CTA's)
 //   warps 2..5  : epilogue - tcgen05.ld the accumulator, round to bf16, transform, store
+//                 (GEGLU mode: warps 2..9, two per tensor-memory lane quarter, each taking one
+//                 64-column half of the tile's output; with four warps that epilogue, a GELU per
+//                 element, ran about as long as a 768-deep main loop and lost 4 % on pairs)
 // Tensor memory holds two 256-column accumulators, so the epilogue of tile i
 // overlaps the main loop of tile i+1.  The k loop runs over 64-wide blocks through
 // a ring of stage buffers guarded by full/empty mbarriers.
@@ -23,7 +26,8 @@
 // matching 128 gate columns (rows I + n0.. of Wi; in a pair, the odd CTA's half of B); the
 // epilogue rounds both to bf16, as the unfused path materialises them, and writes gelu(a) * gate.
 //
-// RESIDUAL mode in a pair streams the residual tile X through shared memory: each epilogue warp
+// RESIDUAL in place (C is X) never reads X: the plain epilogue with TMA reduce-adds for stores.
+// RESIDUAL out of place in a pair streams the residual tile X through shared memory: each epilogue warp
 // keeps four 32-row x 64-column buffers; its elected lane TMA-loads X blocks two ahead of use,
 // every lane adds its accumulator row to its row of the block in place (swizzled, conflict free)
 // and the same buffer is handed to a TMA store.  No global load latency and no transposition is
@@ -44,7 +48,6 @@ constexpr int BM = 128;   // rows per CTA
 constexpr int BN = 256;   // accumulator columns per tile
 constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int GEMM_THREADS = 192;
 constexpr int OUT_STAGE_BYTES = 32 * 128;  // one warp's 32 rows x 64 bf16 columns
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int X_LOOKAHEAD = 2;  // residual blocks in flight ahead of the one being added
@@ -61,8 +64,13 @@ struct GemmCfg {
   static constexpr int B_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = PAIR ? (XTMA ? 5 : 6) : 4;
-  static constexpr int OUT_BUFS = XTMA ? 4 : 2;                // staging buffers per epilogue warp
-  static constexpr int OUT_BYTES = 4 * OUT_BUFS * OUT_STAGE_BYTES;
+  // The GEGLU epilogue (a GELU per output element) is the one whose length rivals a tile's main
+  // loop: it gets eight warps, two per tensor-memory lane quarter, each taking one 64-column half
+  // of the tile's 128 output columns.
+  static constexpr int EPI_WARPS = MODE == GEMM_GEGLU ? 8 : 4;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+  static constexpr int OUT_BUFS = XTMA ? 4 : (EPI_WARPS == 8 ? 1 : 2);  // staging buffers per epilogue warp
+  static constexpr int OUT_BYTES = EPI_WARPS * OUT_BUFS * OUT_STAGE_BYTES;
   // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2],
   // x_full[4 warps][4 buffers]; then the tensor-memory base address
   static constexpr int BAR_FULL = 0, BAR_EMPTY = STAGES, BAR_TFULL = 2 * STAGES, BAR_TEMPTY = 2 * STAGES + 2,
@@ -84,7 +92,7 @@ struct RopeArgs {
 };
 
 template <int MODE, bool PAIR>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__((GemmCfg<MODE, PAIR>::THREADS), 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
                     int M, int n_out, int K, int gate_row0, int num_m, int num_n, RopeArgs rope,
@@ -117,8 +125,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     mbar_init(bar(Cfg::BAR_TFULL), 1);
     mbar_init(bar(Cfg::BAR_TFULL + 1), 1);
-    mbar_init(bar(Cfg::BAR_TEMPTY), PAIR ? 8 : 4);  // one arrival per epilogue warp (of both CTAs)
-    mbar_init(bar(Cfg::BAR_TEMPTY + 1), PAIR ? 8 : 4);
+    mbar_init(bar(Cfg::BAR_TEMPTY), (PAIR ? 2 : 1) * Cfg::EPI_WARPS);  // one arrival per epilogue warp (of both CTAs)
+    mbar_init(bar(Cfg::BAR_TEMPTY + 1), (PAIR ? 2 : 1) * Cfg::EPI_WARPS);
     for (int i = 0; i < 16; ++i) mbar_init(bar(Cfg::BAR_XFULL + i), 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -228,10 +236,10 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // per instruction; the TMA store keeps the load/store unit out of the way and clips rows
     // and columns that fall outside C.
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
-    const uint32_t stage0 = out_base + q * Cfg::OUT_BUFS * OUT_STAGE_BYTES;
+    const uint32_t stage0 = out_base + (warp - 2) * Cfg::OUT_BUFS * OUT_STAGE_BYTES;
     uint32_t ob = 0;  // staging buffer in use
     auto emit64 = [&](const uint32_t (&lo)[32], const uint32_t (&hi)[32], int col, int row0) {
-      if (lane == 0) tma_store_wait_read<1>();  // the buffer used two stores ago is free again
+      if (lane == 0) tma_store_wait_read<Cfg::OUT_BUFS - 1>();  // the buffer about to be written is free again
       __syncwarp();
       const uint32_t dst = stage0 + ob * OUT_STAGE_BYTES + lane * 128;
 #pragma unroll
@@ -256,7 +264,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         else tma_store_2d(&tmC, stage0 + ob * OUT_STAGE_BYTES, col, row0);
         tma_store_commit();
       }
-      ob ^= 1u;
+      ob = (ob + 1u) % Cfg::OUT_BUFS;
     };
     // GEMM_RESIDUAL: the warp's 32 x 64 block of X, fetched coalesced (instruction i covers rows
     // 4i..4i+3) one block ahead of its use; with full 256-column tiles the chain runs across
@@ -519,8 +527,9 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       } else {
         const int col0 = nt * 128;
+        const int c_first = (warp - 2) >> 2;  // eight warps: this one's 64-column half of the tile
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        for (int c = c_first; c < c_first + 1; ++c) {
           const int col = col0 + c * 64;
           if (col >= n_out) break;
           uint32_t lo[32], hi[32];
@@ -600,7 +609,7 @@ static int launch_gemm_as(const void* A, const void* W, void* C, int64_t M, int 
     const long long pairs = std::min<long long>(tiles, sm_count() / 2);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs));
-    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.blockDim = dim3(Cfg::THREADS);
     cfg.dynamicSmemBytes = Cfg::SMEM;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -614,7 +623,7 @@ static int launch_gemm_as(const void* A, const void* W, void* C, int64_t M, int 
                                rope, (int*)status));
   } else {
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(tmA, tmB, tmC, tmX, (int)M, n_out, K, gate_row0,
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tmA, tmB, tmC, tmX, (int)M, n_out, K, gate_row0,
                                                     num_m, num_n, rope, status);
   }
   PE_LAUNCH_CHECK("gemm_bf16_tn_kernel");
@@ -625,14 +634,8 @@ template <int MODE>
 static int launch_gemm(const void* A, const void* W, void* C, int64_t M, int n_out, int K,
                        int w_rows, int gate_row0, RopeArgs rope, int32_t* status,
                        cudaStream_t stream) {
-  // A pair needs more than one CTA's worth of rows to be worth its second CTA.  The GEGLU
-  // epilogue (a GELU per output element) takes about as long as a 768-deep tile's main loop;
-  // coupled to its peer's, as the shared accumulator hand-over couples them, it then runs slower
-  // than on independent CTAs (0.856 against 0.823 ms at 306,851 x 2304 x 768), so that mode
-  // joins the pairs only from K = 1024 on, where the main loop hides it (1.98 against 2.04 ms at
-  // 262,144 x 5248 x 1024, 4.47 against 4.84 ms at 262,144 x 7680 x 1792).
-  const bool pair_pays = MODE != GEMM_GEGLU || K >= 1024;
-  if (pair_pays && M > 2 * BM && g_gemm_pair.load(std::memory_order_relaxed) != 0)
+  // A pair needs more than one CTA's worth of rows to be worth its second CTA.
+  if (M > 2 * BM && g_gemm_pair.load(std::memory_order_relaxed) != 0)
     return launch_gemm_as<MODE, true>(A, W, C, M, n_out, K, w_rows, gate_row0, rope, status, stream);
   return launch_gemm_as<MODE, false>(A, W, C, M, n_out, K, w_rows, gate_row0, rope, status, stream);
 }
