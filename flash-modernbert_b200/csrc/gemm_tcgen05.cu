@@ -64,10 +64,17 @@ struct GemmCfg {
   static constexpr int B_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = PAIR ? (XTMA ? 5 : 6) : 4;
-  // The GEGLU epilogue (a GELU per output element) is the one whose length rivals a tile's main
-  // loop: it gets eight warps, two per tensor-memory lane quarter, each taking one 64-column half
-  // of the tile's 128 output columns.
-  static constexpr int EPI_WARPS = MODE == GEMM_GEGLU ? 8 : 4;
+  // WIDE epilogue (GEGLU mode, whose epilogue is the longest: a GELU per output element): eight
+  // warps, two per tensor-memory lane quarter, each owning one 64-column half of the tile's
+  // output.  A warp pulls its 128 accumulator columns into registers in one go and hands the
+  // accumulator back to the MMA thread at once, before it rounds, transforms and stores anything.
+  // Measured at 306,851 x 2304 x 768: 0.758 ms against 0.785 ms with the accumulator held through
+  // the epilogue (and 0.826 ms before the GELU went to packed fp32 instructions).  The same form
+  // was tried for the other modes and was no faster (plain, RoPE) or slower (reduce-add: 0.303
+  // against 0.285 ms), so they keep four warps that walk the tile in 64-column chunks and release
+  // the accumulator after the last chunk's tensor-memory load.
+  static constexpr bool WIDE = MODE == GEMM_GEGLU;
+  static constexpr int EPI_WARPS = WIDE ? 8 : 4;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int OUT_BUFS = XTMA ? 4 : (EPI_WARPS == 8 ? 1 : 2);  // staging buffers per epilogue warp
   static constexpr int OUT_BYTES = EPI_WARPS * OUT_BUFS * OUT_STAGE_BYTES;
@@ -315,11 +322,25 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int row0 = m0 + q * 32;
       const int row = row0 + lane;
       const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      // Hands the accumulator back to the MMA thread: as soon as a warp has read all it needs of it.
+      auto release_acc = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {  // the accumulator is free again: tell the (leader's) MMA thread
+          if (cta_rank == 0) mbar_arrive(bar(Cfg::BAR_TEMPTY + acc));
+          else mbar_arrive_cluster(cluster_map(bar(Cfg::BAR_TEMPTY + acc), 0));
+        }
+      };
+      const int half = (warp - 2) >> 2;  // WIDE (GEGLU) mode: which 64 output columns this warp owns
       if constexpr (MODE == GEMM_QKV_ROPE) {
         // One 64-column head at a time: rotate the (j, j + 32) pairs of q and k heads by the
         // row's position, on values rounded to bf16 first (as the unfused path stores them).
         const int col0 = nt * BN;
-        uint4 cs[8];  // cos[0..31] then sin[0..31] of this row's position, bf16
+        // cos[0..31] and sin[0..31] of this row's position, widened to fp32 once per tile (its four
+        // heads share them).  The epilogue's instruction count shows in this kernel's time
+        // (skipping the rotation saves 0.06 of 0.85 ms at 306,851 rows), so the rotation below
+        // works on two pairs at a time with the packed fp32 instructions of sm_100.
+        float2 cf[16], sf[16];
         if (col0 < rope.rope_cols) {
           int64_t p = row < M ? rope.pos[row] : 0;
           if (p < 0 || p >= rope.max_positions) {
@@ -328,7 +349,15 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           const uint4* trow = reinterpret_cast<const uint4*>(rope.table + p * 64);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) cs[i] = __ldg(trow + i);
+          for (int i = 0; i < 4; ++i) {
+            const uint4 cw = __ldg(trow + i), sw = __ldg(trow + 4 + i);
+            const uint32_t c4[4] = {cw.x, cw.y, cw.z, cw.w}, s4[4] = {sw.x, sw.y, sw.z, sw.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {  // a 32-bit word holds the values of pairs 8i + 2e and 8i + 2e + 1
+              cf[i * 4 + e] = make_float2(__uint_as_float(c4[e] << 16), __uint_as_float(c4[e] & 0xffff0000u));
+              sf[i * 4 + e] = make_float2(__uint_as_float(s4[e] << 16), __uint_as_float(s4[e] & 0xffff0000u));
+            }
+          }
         }
 #pragma unroll 1
         for (int hp = 0; hp < BN / 64; ++hp) {
@@ -338,15 +367,25 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld_32x32(t_addr + hp * 64, lo);
           tmem_ld_32x32(t_addr + hp * 64 + 32, hi);
           tmem_ld_wait();
+          if (hp == BN / 64 - 1 || col + 64 >= n_out) release_acc();  // the whole accumulator has been read
           if (col < rope.rope_cols) {
-            const __nv_bfloat16* cb = reinterpret_cast<const __nv_bfloat16*>(cs);
+            // Pairs (i, i + 1) of (dim j, dim j + 32): both values rounded to bf16 first (as the
+            // unfused path stores the projection), then exactly rope_pair()'s arithmetic:
+            // lo' = fma(lo, c, -(hi * s)), hi' = fma(hi, c, lo * s), each product and sum rounded once.
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              float ol, oh;
-              rope_pair(round_bf16(__uint_as_float(lo[i])), round_bf16(__uint_as_float(hi[i])),
-                        __bfloat162float(cb[i]), __bfloat162float(cb[32 + i]), ol, oh);
-              lo[i] = __float_as_uint(ol);
-              hi[i] = __float_as_uint(oh);
+            for (int i = 0; i < 32; i += 2) {
+              const uint32_t lw = pack_bf16(__uint_as_float(lo[i]), __uint_as_float(lo[i + 1]));
+              const uint32_t hw = pack_bf16(__uint_as_float(hi[i]), __uint_as_float(hi[i + 1]));
+              const float2 l2 = make_float2(__uint_as_float(lw << 16), __uint_as_float(lw & 0xffff0000u));
+              const float2 h2 = make_float2(__uint_as_float(hw << 16), __uint_as_float(hw & 0xffff0000u));
+              const float2 c2 = cf[i >> 1], s2 = sf[i >> 1];
+              const float2 ns2 = make_float2(-s2.x, -s2.y);
+              const float2 ol = __ffma2_rn(l2, c2, __fmul2_rn(h2, ns2));
+              const float2 oh = __ffma2_rn(h2, c2, __fmul2_rn(l2, s2));
+              lo[i] = __float_as_uint(ol.x);
+              lo[i + 1] = __float_as_uint(ol.y);
+              hi[i] = __float_as_uint(oh.x);
+              hi[i + 1] = __float_as_uint(oh.y);
             }
           }
           emit64(lo, hi, col, row0);
@@ -523,38 +562,38 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld_32x32(t_addr + c * 64, lo);
           tmem_ld_32x32(t_addr + c * 64 + 32, hi);
           tmem_ld_wait();
+          if (c == BN / 64 - 1 || col + 64 >= n_out) release_acc();  // the whole accumulator has been read
           emit64(lo, hi, col, row0);
         }
       } else {
-        const int col0 = nt * 128;
-        const int c_first = (warp - 2) >> 2;  // eight warps: this one's 64-column half of the tile
-#pragma unroll 1
-        for (int c = c_first; c < c_first + 1; ++c) {
-          const int col = col0 + c * 64;
-          if (col >= n_out) break;
-          uint32_t lo[32], hi[32];
+        // this warp's 64 output columns: gelu input columns [64 half, 64 half + 64) and the gate
+        // columns 128 further on
+        const int col = nt * 128 + half * 64;
+        uint32_t va[2][32], vg[2][32];
+        tmem_ld_32x32(t_addr + half * 64, va[0]);
+        tmem_ld_32x32(t_addr + half * 64 + 32, va[1]);
+        tmem_ld_32x32(t_addr + 128 + half * 64, vg[0]);
+        tmem_ld_32x32(t_addr + 128 + half * 64 + 32, vg[1]);
+        tmem_ld_wait();
+        release_acc();
+        if (col < n_out) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            uint32_t va[32], vg[32];
-            tmem_ld_32x32(t_addr + c * 64 + h * 32, va);
-            tmem_ld_32x32(t_addr + 128 + c * 64 + h * 32, vg);
-            tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const float a = round_bf16(__uint_as_float(va[e]));
-              const float g = round_bf16(__uint_as_float(vg[e]));
-              (h == 0 ? lo : hi)[e] = __float_as_uint(gelu_erf(a) * g);
+            for (int e = 0; e < 32; e += 2) {  // two elements at a time: packed roundings and packed GELU
+              const uint32_t aw = pack_bf16(__uint_as_float(va[h][e]), __uint_as_float(va[h][e + 1]));
+              const uint32_t gw = pack_bf16(__uint_as_float(vg[h][e]), __uint_as_float(vg[h][e + 1]));
+              const float2 a2 = make_float2(__uint_as_float(aw << 16), __uint_as_float(aw & 0xffff0000u));
+              const float2 g2 = make_float2(__uint_as_float(gw << 16), __uint_as_float(gw & 0xffff0000u));
+              const float2 o2 = __fmul2_rn(gelu_erf2(a2), g2);
+              va[h][e] = __float_as_uint(o2.x);
+              va[h][e + 1] = __float_as_uint(o2.y);
             }
           }
-          emit64(lo, hi, col, row0);
+          emit64(va[0], va[1], col, row0);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {  // the accumulator is free again: tell the (leader's) MMA thread
-        if (cta_rank == 0) mbar_arrive(bar(Cfg::BAR_TEMPTY + acc));
-        else mbar_arrive_cluster(cluster_map(bar(Cfg::BAR_TEMPTY + acc), 0));
-      }
+      if constexpr (MODE == GEMM_RESIDUAL || MODE == GEMM_L2NORM) release_acc();
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }

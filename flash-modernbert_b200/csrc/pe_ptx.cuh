@@ -321,6 +321,31 @@ __device__ __forceinline__ float gelu_erf(float a) {
   return a * (a >= 0.f ? 1.0f - q : q);
 }
 
+// gelu_erf on two values at once with the packed fp32 instructions of sm_100 (FMUL2 / FFMA2):
+// component for component the same operations in the same order as gelu_erf, hence the same bits,
+// in about three quarters of the instructions.  For epilogues whose instruction count is on the
+// kernel's critical path.
+__device__ __forceinline__ float2 gelu_erf2(float2 a) {
+  const float2 x = __fmul2_rn(make_float2(fabsf(a.x), fabsf(a.y)),
+                              make_float2(0.70710678118654752440f, 0.70710678118654752440f));
+  const float2 d = __ffma2_rn(make_float2(0.3275911f, 0.3275911f), x, make_float2(1.0f, 1.0f));
+  float2 t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.x) : "f"(d.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.y) : "f"(d.y));
+  float2 p = __ffma2_rn(make_float2(1.061405429f, 1.061405429f), t, make_float2(-1.453152027f, -1.453152027f));
+  p = __ffma2_rn(p, t, make_float2(1.421413741f, 1.421413741f));
+  p = __ffma2_rn(p, t, make_float2(-0.284496736f, -0.284496736f));
+  p = __ffma2_rn(p, t, make_float2(0.254829592f, 0.254829592f));
+  p = __fmul2_rn(p, t);
+  const float2 arg = __fmul2_rn(__fmul2_rn(x, x), make_float2(-1.4426950408889634f, -1.4426950408889634f));
+  float2 e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(arg.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(arg.y));
+  const float2 q = __fmul2_rn(__fmul2_rn(make_float2(0.5f, 0.5f), p), e);
+  const float2 r = make_float2(a.x >= 0.f ? 1.0f - q.x : q.x, a.y >= 0.f ? 1.0f - q.y : q.y);
+  return __fmul2_rn(a, r);
+}
+
 // max of three in one instruction (sm_100 has a three-input FMNMX).
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
