@@ -719,9 +719,9 @@ def run_arm(args, impl: str) -> None:
         cpu = cpu_baseline_hf_eager(arch, seqs)
         base.update({
             "value": cpu["value"], "ms_per_step": None, "dtype": "f32", "cpu_baseline": cpu,
-            "config": {"workload": workload_text(args.workload),
-                       "reference_path": "Hugging Face eager fp32 on the host cores (the reference's own oracle, "
-                                         f"packed_encoders/validate.py:150-160); its GPU path did not run: {why}"},
+            "config": {"workload": workload_text(args.workload)},
+            "reference_path": "Hugging Face eager fp32 on the host cores (the reference's own oracle, "
+                              f"packed_encoders/validate.py:150-160); its GPU path did not run: {why}",
             "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         })
         print(json.dumps(base), flush=True)
@@ -746,7 +746,8 @@ def run_arm(args, impl: str) -> None:
         extras = []
 
     if impl == "reference":
-        base["config"]["reference_path"] = (
+        # beside `config`, not inside it: the two arms' `config` objects are identical
+        base["reference_path"] = (
             f"packed_encoders.forward.packed_forward on the GPU (flash kind: {kind}; Triton LN/GeGLU, CuteDSL RoPE, "
             "cuBLAS GEMMs), one replica per GPU")
         base["e2e"] = {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
