@@ -126,3 +126,13 @@ def test_forward_with_the_pooling_head_fused_into_the_final_norm(pe, cuda_device
         assert torch.equal(got, expected)          # no summation involved: same bits
     again = pe.packed_forward_pooled(gpu, params, *batch.forward_args(), pool=pool, normalize=normalize)
     assert torch.equal(again, got)                 # fixed summation order
+    # with the residual adds left to add+LN kernels (the MLP residual then reaches the final norm
+    # as a pending add) the hidden state is the same, so the embeddings are too
+    from flash_modernbert_b200 import _lib
+    lib = _lib.load()
+    try:
+        assert lib.pe_set_option(_lib.OPT_FUSED_RESIDUAL, 0) == 0
+        unfused = pe.packed_forward_pooled(gpu, params, *batch.forward_args(), pool=pool, normalize=normalize)
+    finally:
+        lib.pe_set_option(_lib.OPT_FUSED_RESIDUAL, 1)
+    assert torch.equal(unfused, got)
