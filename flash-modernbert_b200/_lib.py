@@ -32,7 +32,6 @@ OPT_FUSED_GEGLU = 1
 OPT_FUSED_ROPE = 2
 OPT_GEMM_PAIR = 3
 OPT_FUSED_RESIDUAL = 4
-OPT_RESIDUAL_REDUCE = 5
 
 
 class NativeLibraryError(PackedEncodersError):

@@ -11,12 +11,10 @@ namespace pe {
 // Read once at the top of a forward, so a switch flipped by another thread never changes the
 // op list of a forward that is already being enqueued.
 static std::atomic<int> g_options[OPT_COUNT] = {{0}, /*OPT_FUSED_GEGLU*/ {1}, /*OPT_FUSED_ROPE*/ {1},
-                                                /*OPT_GEMM_PAIR*/ {1}, /*OPT_FUSED_RESIDUAL*/ {1},
-                                                /*OPT_RESIDUAL_REDUCE*/ {1}};
+                                                /*OPT_GEMM_PAIR*/ {1}, /*OPT_FUSED_RESIDUAL*/ {1}};
 
 static bool known_option(int key) {
-  return key == OPT_FUSED_GEGLU || key == OPT_FUSED_ROPE || key == OPT_GEMM_PAIR || key == OPT_FUSED_RESIDUAL ||
-         key == OPT_RESIDUAL_REDUCE;
+  return key == OPT_FUSED_GEGLU || key == OPT_FUSED_ROPE || key == OPT_GEMM_PAIR || key == OPT_FUSED_RESIDUAL;
 }
 
 int get_option(int key) { return known_option(key) ? g_options[key].load(std::memory_order_relaxed) : 0; }
@@ -88,7 +86,6 @@ extern "C" int pe_set_option(int key, int value) {
   }
   pe::g_options[key].store(value, std::memory_order_relaxed);
   if (key == pe::OPT_GEMM_PAIR) pe::set_gemm_pair(value);
-  if (key == pe::OPT_RESIDUAL_REDUCE) pe::set_residual_reduce(value);
   return PE_OK;
 }
 

@@ -26,12 +26,9 @@
 // matching 128 gate columns (rows I + n0.. of Wi; in a pair, the odd CTA's half of B); the
 // epilogue rounds both to bf16, as the unfused path materialises them, and writes gelu(a) * gate.
 //
-// RESIDUAL in place (C is X) never reads X: the plain epilogue with TMA reduce-adds for stores.
-// RESIDUAL out of place in a pair streams the residual tile X through shared memory: each epilogue warp
-// keeps four 32-row x 64-column buffers; its elected lane TMA-loads X blocks two ahead of use,
-// every lane adds its accumulator row to its row of the block in place (swizzled, conflict free)
-// and the same buffer is handed to a TMA store.  No global load latency and no transposition is
-// left in the epilogue warps.
+// RESIDUAL mode never reads X: it is the plain epilogue with TMA reduce-adds in place of TMA
+// stores, so the memory system adds the rounded product to what C holds (C is X; out of place the
+// host copies X to C first).
 //
 // Every mbarrier wait is bounded; a wait that gives up records a code in the
 // status word and the CTA unwinds through the common exit, which frees its
@@ -50,20 +47,16 @@ constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int OUT_STAGE_BYTES = 32 * 128;  // one warp's 32 rows x 64 bf16 columns
 constexpr uint32_t TMEM_COLS = 512;
-constexpr int X_LOOKAHEAD = 2;  // residual blocks in flight ahead of the one being added
 
-// GEMM_RESIDUAL_RED: the in-place form of GEMM_RESIDUAL (C is X): the plain epilogue, its TMA stores
-// replaced by TMA reduce-adds, so X is never read by the kernel at all.
-enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2, GEMM_RESIDUAL = 3, GEMM_L2NORM = 4,
-                      GEMM_RESIDUAL_RED = 5 };
+// GEMM_RESIDUAL: the plain epilogue, its TMA stores replaced by TMA reduce-adds (C += bf16(A W^T)).
+enum GemmMode : int { GEMM_PLAIN = 0, GEMM_GEGLU = 1, GEMM_QKV_ROPE = 2, GEMM_RESIDUAL = 3, GEMM_L2NORM = 4 };
 
 template <int MODE, bool PAIR>
 struct GemmCfg {
-  static constexpr bool XTMA = PAIR && MODE == GEMM_RESIDUAL;  // residual blocks arrive by TMA
   static constexpr int B_ROWS = PAIR ? 128 : 256;              // rows of W one CTA stages per k block
   static constexpr int B_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = PAIR ? (XTMA ? 5 : 6) : 4;
+  static constexpr int STAGES = PAIR ? 6 : 4;
   // WIDE epilogue (GEGLU mode, whose epilogue is the longest: a GELU per output element): eight
   // warps, two per tensor-memory lane quarter, each owning one 64-column half of the tile's
   // output.  A warp pulls its 128 accumulator columns into registers in one go and hands the
@@ -76,12 +69,12 @@ struct GemmCfg {
   static constexpr bool WIDE = MODE == GEMM_GEGLU;
   static constexpr int EPI_WARPS = WIDE ? 8 : 4;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-  static constexpr int OUT_BUFS = XTMA ? 4 : (EPI_WARPS == 8 ? 1 : 2);  // staging buffers per epilogue warp
+  static constexpr int OUT_BUFS = EPI_WARPS == 8 ? 1 : 2;  // staging buffers per epilogue warp
   static constexpr int OUT_BYTES = EPI_WARPS * OUT_BUFS * OUT_STAGE_BYTES;
-  // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2],
-  // x_full[4 warps][4 buffers]; then the tensor-memory base address
+  // barrier slots (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then
+  // the tensor-memory base address
   static constexpr int BAR_FULL = 0, BAR_EMPTY = STAGES, BAR_TFULL = 2 * STAGES, BAR_TEMPTY = 2 * STAGES + 2,
-                       BAR_XFULL = 2 * STAGES + 4, BAR_COUNT = 2 * STAGES + 4 + 16;
+                       BAR_COUNT = 2 * STAGES + 4;
   static constexpr int SMEM = STAGES * STAGE_BYTES + OUT_BYTES + 1024 /*align*/ + 8 * BAR_COUNT + 16;
 };
 
@@ -89,9 +82,8 @@ __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
-// Extra operands of the Wqkv + RoPE epilogue and of the residual epilogue.
+// Extra operands of the Wqkv + RoPE epilogue.
 struct RopeArgs {
-  const __nv_bfloat16* residual; // [M, n_out] added to the rounded product (GEMM_RESIDUAL); may alias C
   const int64_t* pos;            // [M] position of each row
   const __nv_bfloat16* table;    // [max_positions, 64]: cos of the 32 frequencies, then sin
   int rope_cols;                 // columns [0, rope_cols) are q and k heads, the rest is v
@@ -101,7 +93,7 @@ struct RopeArgs {
 template <int MODE, bool PAIR>
 __global__ void __launch_bounds__((GemmCfg<MODE, PAIR>::THREADS), 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
+                    const __grid_constant__ CUtensorMap tmC,
                     int M, int n_out, int K, int gate_row0, int num_m, int num_n, RopeArgs rope,
                     int* status) {
   using Cfg = GemmCfg<MODE, PAIR>;
@@ -134,12 +126,10 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     mbar_init(bar(Cfg::BAR_TFULL + 1), 1);
     mbar_init(bar(Cfg::BAR_TEMPTY), (PAIR ? 2 : 1) * Cfg::EPI_WARPS);  // one arrival per epilogue warp (of both CTAs)
     mbar_init(bar(Cfg::BAR_TEMPTY + 1), (PAIR ? 2 : 1) * Cfg::EPI_WARPS);
-    for (int i = 0; i < 16; ++i) mbar_init(bar(Cfg::BAR_XFULL + i), 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmC);
-    if (Cfg::XTMA) tma_prefetch_desc(&tmX);
   }
   if (warp == 1) {
     if (PAIR) {
@@ -267,52 +257,12 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        if constexpr (MODE == GEMM_RESIDUAL_RED) tma_reduce_add_2d(&tmC, stage0 + ob * OUT_STAGE_BYTES, col, row0);
+        if constexpr (MODE == GEMM_RESIDUAL) tma_reduce_add_2d(&tmC, stage0 + ob * OUT_STAGE_BYTES, col, row0);
         else tma_store_2d(&tmC, stage0 + ob * OUT_STAGE_BYTES, col, row0);
         tma_store_commit();
       }
       ob = (ob + 1u) % Cfg::OUT_BUFS;
     };
-    // GEMM_RESIDUAL: the warp's 32 x 64 block of X, fetched coalesced (instruction i covers rows
-    // 4i..4i+3) one block ahead of its use; with full 256-column tiles the chain runs across
-    // tiles, so no fetch latency is exposed after the first tile.
-    uint4 xr[2][8];
-    auto fetch_x = [&](uint4 (&dst)[8], int r0, int col) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int r = r0 + i * 4 + (lane >> 3);
-        const int cc = col + (lane & 7) * 8;
-        dst[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (r < M && cc + 8 <= n_out)
-          dst[i] = *reinterpret_cast<const uint4*>(rope.residual + size_t(r) * n_out + cc);
-      }
-    };
-    const bool res_chain = (MODE == GEMM_RESIDUAL) && (n_out % BN == 0);
-    bool res_ready = false;
-    // XTMA: this warp's stream of residual blocks (32 rows x 64 columns each), numbered across
-    // tiles; block n lives in buffer n & 3 and completes phase (n >> 2) & 1 of that buffer's
-    // barrier.  The elected lane keeps X_LOOKAHEAD blocks in flight.
-    uint32_t xn = 0;            // blocks consumed so far
-    int xl_tile = first_tile;   // next block to load: tile and 64-column chunk
-    int xl_c = 0;
-    uint32_t xl_n = 0;          // blocks loaded so far
-    auto x_load_next = [&]() {  // lane 0 only
-      if (xl_tile >= num_tiles) return;
-      const int xm0 = (xl_tile / num_n) * TILE_ROWS + int(cta_rank) * BM + q * 32;
-      const int xcol = (xl_tile % num_n) * BN + xl_c * 64;
-      const uint32_t b = xl_n & 3u;
-      mbar_expect_tx(bar(Cfg::BAR_XFULL + q * 4 + b), OUT_STAGE_BYTES);
-      tma_load_2d(stage0 + b * OUT_STAGE_BYTES, &tmX, bar(Cfg::BAR_XFULL + q * 4 + b), xcol, xm0);
-      ++xl_n;
-      if (++xl_c == BN / 64 || (xl_tile % num_n) * BN + xl_c * 64 >= n_out) {
-        xl_c = 0;
-        xl_tile += tile_stride;
-      }
-    };
-    if (Cfg::XTMA && lane == 0) {
-#pragma unroll 1
-      for (int i = 0; i < X_LOOKAHEAD; ++i) x_load_next();
-    }
     uint32_t acc = 0, acc_phase = 0;
     for (int tile = first_tile; tile < num_tiles; tile += tile_stride) {
       const int m0 = (tile / num_n) * TILE_ROWS + int(cta_rank) * BM;
@@ -390,137 +340,6 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           emit64(lo, hi, col, row0);
         }
-      } else if constexpr (Cfg::XTMA) {
-        // C = bf16(X + bf16(acc)), X streamed through this warp's four staging buffers by TMA.
-        // Lane l owns row l of the block: eight 16-byte chunks at the swizzled offsets a TMA box
-        // uses, so loads and stores are conflict free and the sum is stored from the same buffer.
-        // X may be C: block n is loaded before block n is stored, and no other block overlaps it.
-        const int col0 = nt * BN;
-        bool x_ok = true;
-#pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          const int col = col0 + c * 64;
-          if (col >= n_out) break;
-          const uint32_t b = xn & 3u;
-          const uint32_t buf = stage0 + b * OUT_STAGE_BYTES;
-          uint32_t lo[32], hi[32];
-          tmem_ld_32x32(t_addr + c * 64, lo);
-          tmem_ld_32x32(t_addr + c * 64 + 32, hi);
-          if (x_ok && !mbar_wait(bar(Cfg::BAR_XFULL + q * 4 + b), (xn >> 2) & 1u, status, ST_GEMM_EPILOGUE_TIMEOUT))
-            x_ok = false;
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t addr = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
-            uint4 xv;
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(xv.x), "=r"(xv.y), "=r"(xv.z), "=r"(xv.w)
-                         : "r"(addr));
-            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
-            uint32_t o[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 xf = __bfloat1622float2(xp[e]);
-              const uint32_t* src = j < 4 ? lo : hi;
-              const float a0 = round_bf16(__uint_as_float(src[(j & 3) * 8 + 2 * e]));
-              const float a1 = round_bf16(__uint_as_float(src[(j & 3) * 8 + 2 * e + 1]));
-              o[e] = pack_bf16(xf.x + a0, xf.y + a1);
-            }
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]),
-                         "r"(o[2]), "r"(o[3])
-                         : "memory");
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          ++xn;
-          if (lane == 0) {
-            if (x_ok) tma_store_2d(&tmC, buf, col, row0);
-            tma_store_commit();
-            // Block xn + 1 goes into the buffer that held block xn - 3, whose store is two
-            // commits back: wait until at most the two newest stores still read their buffers.
-            tma_store_wait_read<2>();
-            if (x_ok) x_load_next();
-          }
-        }
-        if (!x_ok) break;
-      } else if constexpr (MODE == GEMM_RESIDUAL) {
-        // C = bf16(X + bf16(acc)).  The warp fetches its 32 x 64 block of X coalesced (four rows
-        // per instruction), one block ahead of the accumulator it belongs to, turns it into
-        // row-per-thread form through the staging buffer, adds, and stores the sum from the
-        // same buffer.  X may be C: every block is read before the same warp overwrites it.
-        const int col0 = nt * BN;
-        {  // warm L2 with this thread's row of the X tile this CTA handles next: by then the
-           // block fetches below find it on chip instead of paying a DRAM round trip per block
-          const int next = tile + gridDim.x;
-          if (next < num_tiles) {
-            const int nr = (next / num_n) * BM + q * 32 + lane;
-            const int nc = (next % num_n) * BN;
-            if (nr < M) {
-#pragma unroll
-              for (int c = 0; c < BN / 64; ++c)
-                if (nc + c * 64 < n_out)
-                  asm volatile("prefetch.global.L2 [%0];" ::"l"(rope.residual + size_t(nr) * n_out + nc + c * 64));
-            }
-          }
-        }
-        if (!res_ready) fetch_x(xr[0], row0, col0);  // first tile, or tiles with a ragged last chunk
-#pragma unroll
-        for (int c = 0; c < BN / 64; ++c) {
-          const int col = col0 + c * 64;
-          if (col >= n_out) break;
-          if (c + 1 < BN / 64) {
-            fetch_x(xr[(c + 1) & 1], row0, col + 64);
-          } else if (res_chain) {  // last chunk: start on the first block of this CTA's next tile
-            const int next = tile + gridDim.x;
-            if (next < num_tiles) fetch_x(xr[0], (next / num_n) * BM + q * 32, (next % num_n) * BN);
-          }
-          uint32_t lo[32], hi[32];
-          tmem_ld_32x32(t_addr + c * 64, lo);
-          tmem_ld_32x32(t_addr + c * 64 + 32, hi);
-          tmem_ld_wait();
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-          const uint32_t buf = stage0 + ob * OUT_STAGE_BYTES;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = i * 4 + (lane >> 3);
-            const uint4 v = xr[c & 1][i];
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(
-                             buf + r * 128 + (((lane & 7) ^ (r & 7)) << 4)),
-                         "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                         : "memory");
-          }
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t addr = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
-            uint4 xv;
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(xv.x), "=r"(xv.y), "=r"(xv.z), "=r"(xv.w)
-                         : "r"(addr));
-            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
-            uint32_t o[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 xf = __bfloat1622float2(xp[e]);
-              const uint32_t* src = j < 4 ? lo : hi;
-              const float a0 = round_bf16(__uint_as_float(src[(j & 3) * 8 + 2 * e]));
-              const float a1 = round_bf16(__uint_as_float(src[(j & 3) * 8 + 2 * e + 1]));
-              o[e] = pack_bf16(xf.x + a0, xf.y + a1);
-            }
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]),
-                         "r"(o[2]), "r"(o[3])
-                         : "memory");
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tmC, buf, col, row0);
-            tma_store_commit();
-          }
-          ob ^= 1u;
-        }
-        res_ready = res_chain;
       } else if constexpr (MODE == GEMM_L2NORM) {
         // Projection head: at most 256 output columns, so the tile holds whole rows and each
         // thread can L2-normalise its own.  Two passes over the accumulator: the norm of the
@@ -593,7 +412,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           emit64(va[0], va[1], col, row0);
         }
       }
-      if constexpr (MODE == GEMM_RESIDUAL || MODE == GEMM_L2NORM) release_acc();
+      if constexpr (MODE == GEMM_L2NORM) release_acc();
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -614,8 +433,6 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 static std::atomic<int> g_gemm_pair{1};
 void set_gemm_pair(int on) { g_gemm_pair.store(on, std::memory_order_relaxed); }
-static std::atomic<int> g_residual_reduce{1};
-void set_residual_reduce(int on) { g_residual_reduce.store(on, std::memory_order_relaxed); }
 
 template <int MODE, bool PAIR>
 static int launch_gemm_as(const void* A, const void* W, void* C, int64_t M, int n_out, int K,
@@ -634,11 +451,6 @@ static int launch_gemm_as(const void* A, const void* W, void* C, int64_t M, int 
   CUtensorMap tmC;  // output, stored in 32-row x 64-column boxes
   rc = make_tmap_bf16_2d(&tmC, C, (uint64_t)M, (uint64_t)n_out, (uint64_t)n_out, 32);
   if (rc != PE_OK) return rc;
-  CUtensorMap tmX = tmC;  // residual, loaded in the same boxes (RESIDUAL mode in a pair)
-  if (Cfg::XTMA) {
-    rc = make_tmap_bf16_2d(&tmX, rope.residual, (uint64_t)M, (uint64_t)n_out, (uint64_t)n_out, 32);
-    if (rc != PE_OK) return rc;
-  }
   const int tile_rows = PAIR ? 2 * BM : BM;
   const int num_m = int((M + tile_rows - 1) / tile_rows);
   const int cols_per_tile = GEGLU ? 128 : BN;
@@ -658,11 +470,11 @@ static int launch_gemm_as(const void* A, const void* W, void* C, int64_t M, int 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    PE_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmX, (int)M, n_out, K, gate_row0, num_m, num_n,
+    PE_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, (int)M, n_out, K, gate_row0, num_m, num_n,
                                rope, (int*)status));
   } else {
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tmA, tmB, tmC, tmX, (int)M, n_out, K, gate_row0,
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM, stream>>>(tmA, tmB, tmC, (int)M, n_out, K, gate_row0,
                                                     num_m, num_n, rope, status);
   }
   PE_LAUNCH_CHECK("gemm_bf16_tn_kernel");
@@ -710,8 +522,7 @@ extern "C" int pe_gemm_qkv_rope_bf16(const void* A, const void* Wqkv, void* qkv,
   const int n_out = 3 * nh * 64;
   int rc = pe::check_gemm_args(A, Wqkv, qkv, M, n_out, K, "pe_gemm_qkv_rope_bf16");
   if (rc != PE_OK) return rc;
-  pe::RopeArgs rope{nullptr, position_ids, static_cast<const __nv_bfloat16*>(table), 2 * nh * 64,
-                    max_positions};
+  pe::RopeArgs rope{position_ids, static_cast<const __nv_bfloat16*>(table), 2 * nh * 64, max_positions};
   return pe::launch_gemm<pe::GEMM_QKV_ROPE>(A, Wqkv, qkv, M, n_out, K, n_out, 0, rope, status,
                                             static_cast<cudaStream_t>(stream));
 }
@@ -731,15 +542,13 @@ extern "C" int pe_gemm_residual_bf16(const void* A, const void* W, const void* X
   int rc = pe::check_gemm_args(A, W, C, M, Nout, K, "pe_gemm_residual_bf16");
   if (rc != PE_OK) return rc;
   PE_REQUIRE(X != nullptr && ((uintptr_t)X & 15) == 0, "pe_gemm_residual_bf16: X is NULL or unaligned");
-  pe::RopeArgs args{};
-  args.residual = static_cast<const __nv_bfloat16*>(X);
-  // In place (the forward's case) nothing has to read X: the rounded product is ADDED to it by
-  // TMA reduce-adds, one bf16 add with one rounding per element, exactly the sum above.
-  if (X == C && pe::g_residual_reduce.load(std::memory_order_relaxed) != 0)
-    return pe::launch_gemm<pe::GEMM_RESIDUAL_RED>(A, W, C, M, Nout, K, Nout, 0, args, status,
-                                                  static_cast<cudaStream_t>(stream));
-  return pe::launch_gemm<pe::GEMM_RESIDUAL>(A, W, C, M, Nout, K, Nout, 0, args, status,
-                                            static_cast<cudaStream_t>(stream));
+  // Nothing has to read X: the rounded product is ADDED to what C holds by TMA reduce-adds, one
+  // bf16 add with one rounding per element, exactly the sum above.  Out of place, C first
+  // receives a copy of X on the same stream.
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (X != C)
+    PE_CUDA(cudaMemcpyAsync(C, X, size_t(M) * size_t(Nout) * 2, cudaMemcpyDeviceToDevice, st));
+  return pe::launch_gemm<pe::GEMM_RESIDUAL>(A, W, C, M, Nout, K, Nout, 0, pe::RopeArgs{}, status, st);
 }
 
 extern "C" int pe_gemm_l2norm_bf16(const void* A, const void* W, void* C, int64_t M, int Nout, int K,

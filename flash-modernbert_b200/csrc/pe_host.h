@@ -75,10 +75,8 @@ int final_ln_pool(const void* x, const void* w, float eps, const int32_t* cu_seq
                   void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 // Process-wide switches (pe_set_option).
-enum Option : int { OPT_FUSED_GEGLU = 1, OPT_FUSED_ROPE = 2, OPT_GEMM_PAIR = 3, OPT_FUSED_RESIDUAL = 4,
-                    OPT_RESIDUAL_REDUCE = 5, OPT_COUNT = 6 };
-void set_gemm_pair(int on);        // gemm_tcgen05.cu: CTA-pair tiles on (default) or off
-void set_residual_reduce(int on);  // gemm_tcgen05.cu: in-place residual GEMM by TMA reduce-add (default) or by reading X
+enum Option : int { OPT_FUSED_GEGLU = 1, OPT_FUSED_ROPE = 2, OPT_GEMM_PAIR = 3, OPT_FUSED_RESIDUAL = 4, OPT_COUNT = 5 };
+void set_gemm_pair(int on);  // gemm_tcgen05.cu: CTA-pair tiles on (default) or off
 int get_option(int key);
 
 }  // namespace pe

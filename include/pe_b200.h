@@ -98,10 +98,6 @@ int pe_device_check(void);
  * stream in the GEMM epilogue and the norms run as plain LayerNorms (1), or the projections are
  * materialised and pe_add_ln adds them (0). */
 #define PE_OPT_FUSED_RESIDUAL 4
-/* key 5 (PE_OPT_RESIDUAL_REDUCE, default 1): pe_gemm_residual_bf16 called in place (C == X) adds
- * its rounded product to X with TMA reduce-adds and never reads X (1), or loads X, adds and stores
- * (0).  Same bits: one bf16 add with one rounding per element either way. */
-#define PE_OPT_RESIDUAL_REDUCE 5
 /* A forward reads the switches once, when it starts to enqueue its kernels. */
 int pe_set_option(int key, int value);
 
@@ -199,7 +195,9 @@ int pe_gemm_qkv_rope_bf16(const void* A, const void* Wqkv, void* qkv, int64_t M,
 /* A projection and the residual add that follows it in one kernel:
  * C = bf16(X + bf16(A W^T)), the value packed_encoders/ops.py:303-314 computes as x_new from the
  * materialised projection (packed_encoders/forward.py:216-220 and the deferred MLP residual,
- * 221-225).  X, C: bf16 [M, Nout]; C may be X (in place). */
+ * 221-225).  X, C: bf16 [M, Nout]; C may be X (in place: the kernel then never reads X, it adds
+ * its rounded product to it with TMA reduce-adds; out of place X is first copied to C on the
+ * stream). */
 int pe_gemm_residual_bf16(const void* A, const void* W, const void* X, void* C, int64_t M, int Nout,
                           int K, int32_t* status, void* stream);
 

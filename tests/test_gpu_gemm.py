@@ -160,22 +160,20 @@ def test_cta_pair_and_single_cta_tiles_agree(pe, cuda_device, m):
 
 
 @pytest.mark.parametrize("m,n,k", [(300, 768, 768), (4097, 768, 1152), (129, 1024, 2624), (513, 72, 200)])
-def test_inplace_residual_by_reduce_add_equals_load_add_store(pe, cuda_device, m, n, k):
-    """In place, the residual GEMM adds its rounded product to X with TMA reduce-adds (the memory
-    system performs the bf16 add) instead of reading X. One add with one rounding per element either
-    way: same bits as the form that loads X (`PE_OPT_RESIDUAL_REDUCE` = 0) and as the two-step form."""
-    from flash_modernbert_b200 import _lib, ops
+def test_residual_by_reduce_add_in_and_out_of_place(pe, cuda_device, m, n, k):
+    """The residual GEMM adds its rounded product to what C holds with TMA reduce-adds (the memory
+    system performs the bf16 add) and never reads X; out of place X is copied to C first. One add
+    with one rounding per element: the same bits as the two-step form, in place and out of place,
+    and X is left untouched out of place."""
+    from flash_modernbert_b200 import ops
 
-    lib = _lib.load()
     a, w, a_d, w_d = _inputs(m, n, k, cuda_device, seed=31)
     res = torch.randn(m, n, generator=torch.Generator().manual_seed(32)).to(torch.bfloat16).to(cuda_device)
+    keep = res.clone()
     expected = res + ops._linear(a_d, w_d)
-    by_reduce = ops.linear_residual(a_d, w_d, res.clone(), inplace=True)
-    try:
-        assert lib.pe_set_option(_lib.OPT_RESIDUAL_REDUCE, 0) == 0
-        by_load = ops.linear_residual(a_d, w_d, res.clone(), inplace=True)
-    finally:
-        lib.pe_set_option(_lib.OPT_RESIDUAL_REDUCE, 1)
+    out_of_place = ops.linear_residual(a_d, w_d, res)
+    assert torch.equal(res, keep) and out_of_place.data_ptr() != res.data_ptr()
+    in_place = ops.linear_residual(a_d, w_d, res, inplace=True)
     ops.check_status(cuda_device)
-    assert torch.equal(by_load, expected)
-    assert torch.equal(by_reduce, expected)
+    assert torch.equal(out_of_place, expected)
+    assert torch.equal(in_place, expected) and in_place.data_ptr() == res.data_ptr()
