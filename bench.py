@@ -39,7 +39,7 @@ METRIC = "packed tokens/sec, ModernBERT-base doc encode bf16"
 # DRAM bytes (read + write) of the four GEMM launches of one ModernBERT-base layer per token,
 # measured once with ncu on a 71,567-token slice of the workload. GEMM traffic grows in proportion
 # to the rows, so a full launch is this times its tokens; the JSON line says that it is scaled.
-NCU_GEMM_DRAM_BYTES_PER_TOKEN = 1261.2e6 / 71567
+NCU_GEMM_DRAM_BYTES_PER_TOKEN = 1259.7e6 / 71567
 UNIT = "tokens/s"
 DATA = "synthetic (seeded lengths and token ids, random-init weights normal(0, 0.02))"
 CFG5_TOKEN_BUDGET = 262144
