@@ -49,6 +49,8 @@ constexpr uint32_t G_TMEM_COLS = 256;
 constexpr uint32_t G_S_COL = 0;    // S: columns 0..127
 constexpr uint32_t G_O_COL = 128;  // O: columns 128..191
 constexpr uint32_t G_P_COL = 192;  // P: bf16 pairs, keys 2c and 2c + 1 in column 192 + c
+// How many 16-key groups of P a softmax thread holds in registers before it needs the P buffer.
+constexpr int G_HOLD = 4;
 constexpr float G_RESCALE_LOG2 = 8.0f;  // drift of the maximum that moves the reference
 constexpr float G_REDO_LOG2 = 60.0f;    // drift at which a tile is redone against a new reference
 
@@ -383,17 +385,9 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         };
         // The first 32 keys are exponentiated in the same straight-line stretch as the maximum
         // reduction above, before anything has to wait for the P buffer.
-        uint32_t pk0[8], pk1[8];
-        exp16(0, pk0);
-        exp16(1, pk1);
-        if (j > 0) {
-          // P is a single buffer and O an accumulator: the previous tile's P V must have retired
-          // before P is overwritten (or O rescaled, below).
-          wait(bar(GB_O_FULL), (g - 1) & 1);
-          tc_fence_after();
-        }
-        g_tmem_st8(lane_addr + G_P_COL, pk0);
-        g_tmem_st8(lane_addr + G_P_COL + 8, pk1);
+        uint32_t pkh[G_HOLD][8];  // P of the first 16 * G_HOLD keys, held until the P buffer is free
+        exp16(0, pkh[0]);
+        exp16(1, pkh[1]);
         const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
         // The tile's maximum is known while S is still ours.  If the inherited reference is more
         // than 2^60 below it (or, for an item's first tile, above it), P would overflow (or
@@ -402,6 +396,8 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
                          (m_tile - m_ref > G_REDO_LOG2 || (j == 0 && m_ref - m_tile > G_REDO_LOG2));
         if (__builtin_expect(__any_sync(0xffffffffu, bad), 0)) {
           if (j > 0) {
+            wait(bar(GB_O_FULL), (g - 1) & 1);  // the previous tile's P V has retired: P and O are ours
+            tc_fence_after();
             const float alpha = bad ? g_ex2(m_ref - m_tile) : 1.0f;
             g_rescale_accumulator(lane_addr + G_O_COL, alpha);
             l_run *= alpha;
@@ -431,11 +427,24 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(GB_S_EMPTY));
         } else {
+          // All 128 scores are in registers and will not be read again: the next Q K^T may
+          // overwrite S now.
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(GB_S_EMPTY));  // the next Q K^T may overwrite S now
+          if (lane == 0) mbar_arrive(bar(GB_S_EMPTY));
 #pragma unroll
-          for (int c16 = 2; c16 < 8; ++c16) {
+          for (int c16 = 2; c16 < G_HOLD; ++c16) exp16(c16, pkh[c16]);
+          if (j > 0) {
+            // P is a single buffer: the previous tile's P V must have retired before P is
+            // overwritten.  Holding the first groups of P in registers (which the scores they
+            // were made from no longer need) puts this wait where it no longer waits.
+            wait(bar(GB_O_FULL), (g - 1) & 1);
+            tc_fence_after();
+          }
+#pragma unroll
+          for (int c16 = 0; c16 < G_HOLD; ++c16) g_tmem_st8(lane_addr + G_P_COL + c16 * 8, pkh[c16]);
+#pragma unroll
+          for (int c16 = G_HOLD; c16 < 8; ++c16) {
             uint32_t pk[8];
             exp16(c16, pk);
             g_tmem_st8(lane_addr + G_P_COL + c16 * 8, pk);
