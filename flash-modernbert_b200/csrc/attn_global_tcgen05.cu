@@ -10,8 +10,9 @@
 // 192 threads (168 registers), 113 KB of shared memory and 256 tensor-memory columns:
 //   warps 0..3 : softmax - thread t owns query row t: one tcgen05.ld pass brings its 128
 //                scores into registers (S is released at once, so the next Q K^T overlaps the
-//                exp2 work), row maximum, exp2, row sum; P goes back to TENSOR MEMORY as bf16
-//                pairs (tcgen05.st), never through shared memory
+//                exp2 work), exp2 against an inherited reference exponent, row sum - and no row
+//                maximum: the sum says when the reference has to move; P goes back to TENSOR
+//                MEMORY as bf16 pairs (tcgen05.st), never through shared memory
 //   warp 4     : TMA producer - Q (single buffer), K and V in separate three-deep rings (K is
 //                free as soon as Q K^T retires, so it runs ahead of V)
 //   warp 5     : tensor-memory owner and MMA issuer - S = Q K^T (both operands from shared
@@ -21,10 +22,12 @@
 // Shared memory then carries only Q, K and V: with P there as well, its 128 bytes per clock
 // (operand reads of both products, P written and read back, the TMA fills) were as loaded as
 // the exp2 unit.
-// The output accumulator is rescaled in tensor memory only when a row maximum has grown by
-// more than 2^8 since the maximum it was last scaled to (P then stays below 256, exact
-// enough in bf16 and far from overflow in the fp32 sums); after the first tile or two of an
-// item that almost never happens, so the per-tile loop has no accumulator traffic at all.
+// The output accumulator is rescaled in tensor memory only when a tile's row sum has reached
+// 2^16 against the reference it was exponentiated to (P is bf16 and the sums fp32: both keep
+// their relative precision at any scale, and 2^60 is far from overflow); after the first tile
+// or two of an item that almost never happens, so the per-tile loop has no accumulator traffic
+// at all.  A row sum that shows overflow or underflow sends the warp through an exact by-hand
+// path for that tile (g_tile_by_hand).
 //
 // Rows of a K/V tile outside the sequence (or the band) are whatever TMA fetched and are
 // masked to -inf before the softmax, so P is exactly 0 there.  Query rows past the end of a
@@ -51,8 +54,9 @@ constexpr uint32_t G_O_COL = 128;  // O: columns 128..191
 constexpr uint32_t G_P_COL = 192;  // P: bf16 pairs, keys 2c and 2c + 1 in column 192 + c
 // How many 16-key groups of P a softmax thread holds in registers before it needs the P buffer.
 constexpr int G_HOLD = 4;
-constexpr float G_RESCALE_LOG2 = 8.0f;  // drift of the maximum that moves the reference
-constexpr float G_REDO_LOG2 = 60.0f;    // drift at which a tile is redone against a new reference
+constexpr int G_RESCALE_LOG2_SUM = 16;   // a tile's row sum of 2^16 or more moves the reference
+constexpr float G_SUM_MAX = 1.152921504606846976e18f;   // 2^60: above it (or not finite) the tile is redone
+constexpr float G_SUM_MIN = 8.673617379884035e-19f;     // 2^-60: an item's first tile below it is redone
 
 enum {
   GB_Q_FULL = 0,
@@ -122,10 +126,69 @@ __device__ __noinline__ void g_rescale_accumulator(uint32_t o_addr, float alpha)
   g_tmem_st_wait();
 }
 
+// Rare path of the softmax warps (out of line, with registers of its own): the scores of one
+// query row against the 128 keys of a tile by hand - fp32 dot products of the bf16 inputs in
+// global memory.  Pass 0 takes the row maximum, pass 1 exponentiates against it and writes P
+// one column (two keys) at a time.  Taken only when a tile's row sum shows that P overflowed or
+// vanished against the inherited reference, which needs scores 2^60 apart within a row; every
+// lane of the warp comes here together, lanes that are not `bad` keep their reference.
+struct GByHand {
+  float m_ref, l_run, sum;
+};
+__device__ __noinline__ GByHand g_tile_by_hand(const __nv_bfloat16* qrow, const __nv_bfloat16* k0, int64_t ld, int len,
+                                               int col0, int c_lo, int c_hi, uint32_t lane_addr, float m_ref,
+                                               float l_run, bool bad, bool have_acc) {
+  const float scale_log2 = 0.125f * 1.4426950408889634f;
+  uint4 qv[8];  // the row of q as packed bf16 pairs
+#pragma unroll
+  for (int i = 0; i < 8; ++i) qv[i] = __ldg(reinterpret_cast<const uint4*>(qrow) + i);
+  float m = -INFINITY, sum = 0.f;
+#pragma unroll 1
+  for (int step = 0; step < 128; ++step) {
+    const int cp = step & 63, c = 2 * cp;
+    if (step == 64) {  // between the passes: the new reference, the accumulator moved to it
+      const float m_new = m * scale_log2;
+      const bool move = bad && m > -INFINITY;
+      const float alpha = (move && have_acc) ? g_ex2(m_ref - m_new) : 1.0f;
+      if (have_acc) {
+        g_rescale_accumulator(lane_addr + G_O_COL, alpha);
+        l_run *= alpha;
+      }
+      if (move) m_ref = m_new;
+    }
+    float s01[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int key = min(max(col0 + c + h, 0), len - 1);  // for the address only; validity below
+      const uint4* krow = reinterpret_cast<const uint4*>(k0 + key * ld);
+      float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint4 u = __ldg(krow + i);
+        acc[0] = __ffma2_rn(bf16x2_to_float2(qv[i].x), bf16x2_to_float2(u.x), acc[0]);
+        acc[1] = __ffma2_rn(bf16x2_to_float2(qv[i].y), bf16x2_to_float2(u.y), acc[1]);
+        acc[2] = __ffma2_rn(bf16x2_to_float2(qv[i].z), bf16x2_to_float2(u.z), acc[2]);
+        acc[3] = __ffma2_rn(bf16x2_to_float2(qv[i].w), bf16x2_to_float2(u.w), acc[3]);
+      }
+      const float sc = ((acc[0].x + acc[0].y) + (acc[1].x + acc[1].y)) + ((acc[2].x + acc[2].y) + (acc[3].x + acc[3].y));
+      s01[h] = (c + h >= c_lo && c + h <= c_hi) ? sc : -INFINITY;
+    }
+    if (step < 64) {
+      m = fmax3(m, s01[0], s01[1]);
+    } else {
+      const float p0 = g_ex2(fmaf(s01[0], scale_log2, -m_ref));
+      const float p1 = g_ex2(fmaf(s01[1], scale_log2, -m_ref));
+      sum += p0 + p1;
+      g_tmem_st1(lane_addr + G_P_COL + cp, pack_bf16(p0, p1));
+    }
+  }
+  return GByHand{m_ref, l_run, sum};
+}
+
 __global__ void __launch_bounds__(G_THREADS, 2)
 attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __restrict__ tile_info,
                       const int32_t* __restrict__ total_tiles_ptr, int nh, int half_window,
-                      __nv_bfloat16* __restrict__ out, int* status) {
+                      const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out, int* status) {
   const int total_items = *total_tiles_ptr * nh;
   if (int(blockIdx.x) >= total_items) return;  // whole CTA leaves before any barrier or allocation
 
@@ -324,16 +387,18 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         // fetched) and never stored: masking them would only make their warps diverge.
       }
       // P and the accumulator are scaled to 2^m_ref.  m_ref need not be the running maximum:
-      // fp32 and bf16 carry 8 exponent bits, so any reference within about 2^60 of the
-      // maximum gives the same relative precision.  A tile is therefore exponentiated against
-      // the reference it inherits while its own maximum is still being reduced (the two
-      // instruction streams interleave instead of running one after the other); the maximum
-      // moves the reference afterwards (pending) once it has drifted by more than 2^8.
+      // fp32 and bf16 carry 8 exponent bits, so any reference within about 2^60 of the maximum
+      // gives the same relative precision.  No maximum is taken at all: a tile is exponentiated
+      // against the reference it inherits, and its row sum - which the softmax needs anyway -
+      // bounds its maximum from both sides (max <= sum <= 128 max).  A sum of 2^16 or more moves
+      // the reference up by that power of two at the next tile (pending; the factor is exact).
+      // A sum beyond 2^60, or not finite, or, for an item's first tile, below 2^-60, means that
+      // P has overflowed or vanished: then, and only then, the tile's scores are recomputed by
+      // hand from q and k in global memory and exponentiated against their true maximum.
       float m_ref = 0.f;
       float l_run = 0.f;
-      float m_pend = 0.f;
+      int k_pend = 0;
       bool pend = false;
-
       for (int j = 0; j < n_kv; ++j, ++g, col0 += G_BN) {
         wait(bar(GB_S_FULL), g & 1);
         tc_fence_after();
@@ -345,31 +410,31 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
         const int c_lo = key_lo - col0, c_hi = key_hi - col0;  // valid columns [c_lo, c_hi]
         // warp-uniform, so a warp never runs both branches
         const bool full = __all_sync(0xffffffffu, c_lo <= 0 && c_hi >= G_BN - 1);
-        if (__builtin_expect(__any_sync(0xffffffffu, pend), 0)) {  // rare: move the reference up to the last tile's maximum
-          wait(bar(GB_O_FULL), (g - 1) & 1);  // its P V has retired (pend is never set when j == 0)
+        if (__builtin_expect(__any_sync(0xffffffffu, pend), 0)) {  // rare: move the reference up by 2^k_pend
+          wait(bar(GB_O_FULL), (g - 1) & 1);  // the last tile's P V has retired (pend is never set when j == 0)
           tc_fence_after();
-          const float alpha = pend ? g_ex2(m_ref - m_pend) : 1.0f;
+          const float alpha = pend ? __int_as_float((127 - k_pend) << 23) : 1.0f;
           g_rescale_accumulator(lane_addr + G_O_COL, alpha);
           l_run *= alpha;
-          if (pend) m_ref = m_pend;
+          if (pend) m_ref += float(k_pend);
         }
         tmem_ld_wait();
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one
+        // All 128 scores are in registers and S is not read again: the next Q K^T may overwrite it.
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(GB_S_EMPTY));
         // A tile that is not valid for every row of the warp (the last one of a sequence, every
         // one of a band) first has its invalid scores replaced by -inf, in one block of its own;
-        // the maximum and the exponentials below are then the same code for every tile.  (Separate
-        // unrolled variants per 16-column group were 1 % faster on bands and cost more than that
-        // on full attention by crowding the instruction cache.)
+        // the exponentials below are then the same code for every tile.  (Separate unrolled
+        // variants per 16-column group were 1 % faster on bands and cost more than that on full
+        // attention by crowding the instruction cache.)
         if (__builtin_expect(!full, 0)) {
 #pragma unroll
           for (int c = 0; c < 128; ++c) sv[c] = (c >= c_lo && c <= c_hi) ? sv[c] : 0xff800000u;  // -inf
         }
-#pragma unroll
-        for (int c = 0; c < 128; c += 2)
-          mx4[(c >> 1) & 3] = fmax3(mx4[(c >> 1) & 3], __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
         // Two scores at a time through the packed fp32 instructions of sm_100 (one FFMA2 for
         // the scale-and-shift, one FADD2 for the row sums): the softmax is bound by instruction
-        // issue, and this takes two of the seven instructions per pair out of the loop.
+        // issue.
         float2 sum2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
         const float2 scale2 = make_float2(scale_log2, scale_log2);
         const float2 shift2 = make_float2(-m_ref, -m_ref);
@@ -383,80 +448,46 @@ attn_global_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv, const int4* __
             pk[e >> 1] = pack_bf16(p.x, p.y);
           }
         };
-        // The first 32 keys are exponentiated in the same straight-line stretch as the maximum
-        // reduction above, before anything has to wait for the P buffer.
         uint32_t pkh[G_HOLD][8];  // P of the first 16 * G_HOLD keys, held until the P buffer is free
-        exp16(0, pkh[0]);
-        exp16(1, pkh[1]);
-        const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-        // The tile's maximum is known while S is still ours.  If the inherited reference is more
-        // than 2^60 below it (or, for an item's first tile, above it), P would overflow (or
-        // vanish): move the reference to this maximum and redo the tile from S.
-        const bool bad = (m_tile > -INFINITY) &&
-                         (m_tile - m_ref > G_REDO_LOG2 || (j == 0 && m_ref - m_tile > G_REDO_LOG2));
+#pragma unroll
+        for (int c16 = 0; c16 < G_HOLD; ++c16) exp16(c16, pkh[c16]);
+        if (j > 0) {
+          // P is a single buffer: the previous tile's P V must have retired before P is
+          // overwritten.  Holding the first groups of P in registers (which the scores they
+          // were made from no longer need) puts this wait where it no longer waits.
+          wait(bar(GB_O_FULL), (g - 1) & 1);
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int c16 = 0; c16 < G_HOLD; ++c16) g_tmem_st8(lane_addr + G_P_COL + c16 * 8, pkh[c16]);
+#pragma unroll
+        for (int c16 = G_HOLD; c16 < 8; ++c16) {
+          uint32_t pk[8];
+          exp16(c16, pk);
+          g_tmem_st8(lane_addr + G_P_COL + c16 * 8, pk);
+        }
+        float sum_tile = ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y)) + ((sum2[2].x + sum2[2].y) + (sum2[3].x + sum2[3].y));
+        const bool has_key = full || (c_hi >= 0 && c_lo <= G_BN - 1 && c_hi >= c_lo);
+        const bool bad = !(sum_tile <= G_SUM_MAX) || (j == 0 && has_key && sum_tile < G_SUM_MIN);
         if (__builtin_expect(__any_sync(0xffffffffu, bad), 0)) {
-          if (j > 0) {
-            wait(bar(GB_O_FULL), (g - 1) & 1);  // the previous tile's P V has retired: P and O are ours
-            tc_fence_after();
-            const float alpha = bad ? g_ex2(m_ref - m_tile) : 1.0f;
-            g_rescale_accumulator(lane_addr + G_O_COL, alpha);
-            l_run *= alpha;
-          }
-          if (bad) m_ref = m_tile;
-          float redo_sum = 0.f;
-#pragma unroll 1
-          for (int c8 = 0; c8 < 16; ++c8) {
-            uint32_t v8[8], pk[4];
-            g_tmem_ld8(lane_addr + G_S_COL + c8 * 8, v8);
-            tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-              const int c = c8 * 8 + e;
-              const float s0 = (full || (c >= c_lo && c <= c_hi)) ? __uint_as_float(v8[e]) : -INFINITY;
-              const float s1 = (full || (c + 1 >= c_lo && c + 1 <= c_hi)) ? __uint_as_float(v8[e + 1]) : -INFINITY;
-              const float p0 = g_ex2(fmaf(s0, scale_log2, -m_ref));
-              const float p1 = g_ex2(fmaf(s1, scale_log2, -m_ref));
-              redo_sum += p0 + p1;
-              pk[e >> 1] = pack_bf16(p0, p1);
-            }
-            g_tmem_st4(lane_addr + G_P_COL + c8 * 4, pk);
-          }
-          sum2[0] = make_float2(redo_sum, 0.f);
-          sum2[1] = sum2[2] = sum2[3] = make_float2(0.f, 0.f);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(GB_S_EMPTY));
-        } else {
-          // All 128 scores are in registers and will not be read again: the next Q K^T may
-          // overwrite S now.
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(GB_S_EMPTY));
-#pragma unroll
-          for (int c16 = 2; c16 < G_HOLD; ++c16) exp16(c16, pkh[c16]);
-          if (j > 0) {
-            // P is a single buffer: the previous tile's P V must have retired before P is
-            // overwritten.  Holding the first groups of P in registers (which the scores they
-            // were made from no longer need) puts this wait where it no longer waits.
-            wait(bar(GB_O_FULL), (g - 1) & 1);
-            tc_fence_after();
-          }
-#pragma unroll
-          for (int c16 = 0; c16 < G_HOLD; ++c16) g_tmem_st8(lane_addr + G_P_COL + c16 * 8, pkh[c16]);
-#pragma unroll
-          for (int c16 = G_HOLD; c16 < 8; ++c16) {
-            uint32_t pk[8];
-            exp16(c16, pk);
-            g_tmem_st8(lane_addr + G_P_COL + c16 * 8, pk);
-          }
+          g_tmem_st_wait();
+          const int64_t ld = 3 * int64_t(H);
+          const GItem it = g_make_item(__ldg(tile_info + item / nh), item, nh, half_window);
+          const GByHand r = g_tile_by_hand(qkv + (int64_t(it.seq_begin) + min(it.q0 + row, it.len - 1)) * ld + it.head * 64,
+                                           qkv + int64_t(it.seq_begin) * ld + H + it.head * 64, ld, it.len, col0,
+                                           full ? 0 : c_lo, full ? G_BN - 1 : c_hi, lane_addr, m_ref, l_run, bad, j > 0);
+          m_ref = r.m_ref;
+          l_run = r.l_run;
+          sum_tile = r.sum;
         }
         g_tmem_st_wait();
-        l_run += ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y)) + ((sum2[2].x + sum2[2].y) + (sum2[3].x + sum2[3].y));
+        l_run += sum_tile;
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(GB_P_FULL));
-        pend = m_tile > m_ref + G_RESCALE_LOG2;
-        m_pend = m_tile;
+        // floor(log2(sum)) from the exponent field; a sum of 0 gives -127
+        k_pend = (__float_as_int(sum_tile) >> 23) - 127;
+        pend = k_pend >= G_RESCALE_LOG2_SUM && k_pend <= 127;
       }
       {  // the item's accumulator: normalise and store this row
         const GItem it = g_make_item(__ldg(tile_info + item / nh), item, nh, half_window);
@@ -510,6 +541,7 @@ int attn_run_global_tc(const void* qkv, const int4* tile_info, const int32_t* to
   const int64_t slots = 2 * (int64_t)sm_count();  // two resident CTAs per SM
   const int grid = (int)(max_items < slots ? max_items : slots);
   attn_global_tc_kernel<<<grid, G_THREADS, G_SMEM, st>>>(tm, tile_info, total_tiles, nh, half_window,
+                                                        static_cast<const __nv_bfloat16*>(qkv),
                                                         static_cast<__nv_bfloat16*>(out), status);
   PE_LAUNCH_CHECK("attn_global_tc_kernel");
   return PE_OK;

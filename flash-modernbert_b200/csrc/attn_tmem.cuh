@@ -40,6 +40,15 @@ __device__ __forceinline__ void g_tmem_st8(uint32_t taddr, const uint32_t* v) {
                : "memory");
 }
 
+__device__ __forceinline__ void g_tmem_st1(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+
+// two packed bf16 (element 0 in the low half) as fp32
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t u) {
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+
 __device__ __forceinline__ void g_tmem_st4(uint32_t taddr, const uint32_t* v) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(v[0]),
                "r"(v[1]), "r"(v[2]), "r"(v[3])
