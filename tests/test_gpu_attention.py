@@ -103,6 +103,31 @@ def test_row_maximum_drifts_far_between_key_tiles(pe, cuda_device, q_scale):
         assert rep["min_token_cos"] > 0.995 and rep["mean_token_cos"] > 0.9995, (q_scale, hw, rep)
 
 
+def test_window_score_far_above_the_rows_own_keys(pe, cuda_device):
+    """Every query of two interior tiles scores about -1000 against the keys near it (2^-180
+    after scaling) and about 0 against a few keys further back in its window, so a reference
+    exponent taken from nearby keys is off by far more than 2^60.  Sliding-window layers: the
+    cheap unmasked reference is refused and the exact masked maximum taken.  Full attention over
+    the same data: first key tiles vanish against the initial reference, later ones overflow the
+    inherited one - both send the warp through the by-hand path."""
+    qkv, cu = _qkv([900, 260], 4, cuda_device, seed=21)
+    gen = torch.Generator().manual_seed(22)
+    qkv[256:512, 0] = (4.0 + 0.1 * torch.randn(256, 4, 64, generator=gen)).to(torch.bfloat16)
+    qkv[230:512, 1] = (-4.0 + 0.1 * torch.randn(282, 4, 64, generator=gen)).to(torch.bfloat16)
+    qkv[300:330, 1] = (0.02 * torch.randn(30, 4, 64, generator=gen)).to(torch.bfloat16)   # the keys that win
+    qkv[420:424, 1] = (0.02 * torch.randn(4, 4, 64, generator=gen)).to(torch.bfloat16)
+    for hw in (64, None):
+        out = _run(qkv, cu, 4, hw, cuda_device)
+        ref = O.attention(qkv[:, 0], qkv[:, 1], qkv[:, 2], cu, hw, faithful=False)
+        got = out.cpu().float().view_as(ref)
+        assert bool(torch.isfinite(got).all())
+        rep = O.cosine_report(got.reshape(got.shape[0], -1), ref.reshape(ref.shape[0], -1))
+        assert rep["min_token_cos"] > 0.995 and rep["mean_token_cos"] > 0.9995, (hw, rep)
+        # rows that see none of the winning keys are ordinary rows: tight agreement
+        calm = torch.cat([torch.arange(0, 200), torch.arange(600, 1160)])
+        assert float((got[calm] - ref[calm]).abs().max()) < 0.03
+
+
 @pytest.mark.parametrize("half_window", [None, 64])
 def test_no_cross_sequence_leakage(pe, cuda_device, half_window):
     # tests/test_packed_short_attention.py:110-124 of the reference
