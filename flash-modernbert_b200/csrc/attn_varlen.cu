@@ -163,7 +163,7 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
   // flight while this head is computed.  The kernel is latency bound - one short global round
   // trip and a few hundred MMAs per (tile, head) - so what counts is never waiting for that
   // round trip with nothing else to do.  The sequences it serves (at most 64 tokens) have a
-  // single key tile.
+  // single key tile; the shortest of them share their tile among several heads (below).
   constexpr int STAGE_BYTES_ = BM * 128 + 2 * ATT_BN * 128;
   __shared__ __align__(128) uint8_t smem[2 * STAGE_BYTES_];
   const uint32_t smem0 = smem_u32(smem);
@@ -187,30 +187,48 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float scale_log2 = 0.125f * 1.4426950408889634f;
   const int row_in_warp = lane >> 2;           // rows r and r + 8 of this warp's 16
-  const int qrow0 = q0 + warp * 16 + row_in_warp;  // position in sequence of row r
-  // Warps whose 16 rows lie past the end of the sequence only take part in the loads and barriers.
-  const bool active = q0 + warp * 16 < len;
+  // A sequence of at most BM / 2 tokens leaves half of the tile's rows - and warps - without
+  // work.  Such a tile is shared by several heads instead: with R = 16 or 32 rows per head, rows
+  // [R hs, R hs + R) of the Q, K and V tiles belong to head slot hs, and a step of the CTA serves
+  // BM / R of its heads at once (same loads, same shared memory, a quarter or half of the steps).
+  int R = BM;
+  if (q0 == 0 && n_kv == 1) R = len <= 16 ? 16 : (len <= 32 ? min(32, BM) : BM);
+  const int hps = BM / R;                                // heads per step
+  const int hs = (warp * 16) / R, rb = (warp * 16) % R;  // this warp's head slot and first row in it
+  const int qrow0 = q0 + rb + row_in_warp;               // position in sequence of row r
+  const int my_heads = (nh - int(blockIdx.y) + int(gridDim.y) - 1) / int(gridDim.y);  // heads of this CTA
+  auto head_of = [&](int i) { return int(blockIdx.y) + i * int(gridDim.y); };           // the i-th of them
 
-  auto load_head = [&](int head, int stage) {
+  auto load_step = [&](int t, int stage) {
     const uint32_t sQ_ = smem0 + stage * STAGE_BYTES_;
-    const __nv_bfloat16* qg_ = qkv + int64_t(seq_begin) * stride + head * ATT_D;
-    load_tile_async<THREADS>(sQ_, qg_ + int64_t(q0) * stride, stride, BM, len - q0);
-    load_tile_async<THREADS>(sQ_ + BM * 128, qg_ + H + int64_t(kv_lo) * stride, stride, ATT_BN, kv_hi - kv_lo);
-    load_tile_async<THREADS>(sQ_ + BM * 128 + ATT_BN * 128, qg_ + 2 * H + int64_t(kv_lo) * stride, stride,
-                             ATT_BN, kv_hi - kv_lo);
+    for (int s_ = 0; s_ < hps; ++s_) {
+      const bool hv = t * hps + s_ < my_heads;  // slots past the CTA's last head are zero-filled
+      const __nv_bfloat16* qg_ = qkv + int64_t(seq_begin) * stride + (hv ? head_of(t * hps + s_) : 0) * ATT_D;
+      const uint32_t sub = uint32_t(s_ * R) * 128u;
+      load_tile_async<THREADS>(sQ_ + sub, qg_ + int64_t(q0) * stride, stride, R, hv ? len - q0 : 0);
+      load_tile_async<THREADS>(sQ_ + BM * 128 + sub, qg_ + H + int64_t(kv_lo) * stride, stride,
+                               hps == 1 ? ATT_BN : R, hv ? kv_hi - kv_lo : 0);
+      load_tile_async<THREADS>(sQ_ + BM * 128 + ATT_BN * 128 + sub, qg_ + 2 * H + int64_t(kv_lo) * stride, stride,
+                               hps == 1 ? ATT_BN : R, hv ? kv_hi - kv_lo : 0);
+    }
     cp_async_commit();
   };
-  load_head(blockIdx.y, 0);
+  load_step(0, 0);
 
   int stage = 0;
-  for (int head = blockIdx.y; head < nh; head += gridDim.y, stage ^= 1) {
+  for (int t = 0; t * hps < my_heads; ++t, stage ^= 1) {
   const uint32_t sQ = smem0 + stage * STAGE_BYTES_;
   const uint32_t sK = sQ + BM * 128;
   const uint32_t sV = sK + ATT_BN * 128;
+  const bool head_valid = t * hps + hs < my_heads;
+  const int head = head_of(head_valid ? t * hps + hs : 0);
+  // Warps whose 16 rows lie past the end of the sequence (or whose slot holds no head) only take
+  // part in the loads and barriers.
+  const bool active = head_valid && q0 + rb < len;
   const __nv_bfloat16* kg = qkv + int64_t(seq_begin) * stride + head * ATT_D + H;
   const __nv_bfloat16* vg = kg + H;
-  const bool more = head + int(gridDim.y) < nh;
-  if (more) load_head(head + gridDim.y, stage ^ 1);  // the other stage was released by the barrier below
+  const bool more = (t + 1) * hps < my_heads;
+  if (more) load_step(t + 1, stage ^ 1);  // the other stage was released by the barrier below
 
   float o_acc[8][4];
 #pragma unroll
@@ -264,7 +282,7 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
       for (int jp = 0; jp < 4; ++jp) {
         if (jp >= nkb) break;
         const int mid = lane >> 3;
-        const int r = (jp * 2 + (mid >> 1)) * 8 + (lane & 7);
+        const int r = hs * R + (jp * 2 + (mid >> 1)) * 8 + (lane & 7);
         const int c = kk * 2 + (mid & 1);
         uint32_t b0, b1, b2, b3;
         ldsm_x4(kt + tile_off(r, c), b0, b1, b2, b3);
@@ -332,7 +350,7 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
 #pragma unroll
       for (int jp = 0; jp < 4; ++jp) {
         const int mid = lane >> 3;
-        const int r = kk * 16 + (mid & 1) * 8 + (lane & 7);
+        const int r = hs * R + kk * 16 + (mid & 1) * 8 + (lane & 7);
         const int c = jp * 2 + (mid >> 1);
         uint32_t b0, b1, b2, b3;
         ldsm_x4_t(vt + tile_off(r, c), b0, b1, b2, b3);
@@ -361,13 +379,13 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int idx = i * 32 + lane;
-    const int r = warp * 16 + (idx >> 3), c = idx & 7;
-    if (q0 + r < len) {
+    const int r = warp * 16 + (idx >> 3), c = idx & 7;  // row of the tile; rb + (idx >> 3) within the head slot
+    if (active && q0 + rb + (idx >> 3) < len) {
       uint4 v;
       asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                    : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                    : "r"(sQ + tile_off(r, c)));
-      *reinterpret_cast<uint4*>(og + int64_t(q0 + r) * H + c * 8) = v;
+      *reinterpret_cast<uint4*>(og + int64_t(q0 + rb + (idx >> 3)) * H + c * 8) = v;
     }
   }
   __syncthreads();  // every warp is done with this stage before the head after next is loaded into it
