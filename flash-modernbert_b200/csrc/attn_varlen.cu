@@ -143,11 +143,24 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
 template <int THREADS>
 __device__ __forceinline__ void load_tile_async(uint32_t smem_tile, const __nv_bfloat16* gbase,
                                                 int64_t stride, int rows, int valid_rows) {
-  for (int i = threadIdx.x; i < rows * 8; i += THREADS) {
-    const int r = i >> 3, c = i & 7;
-    const bool ok = r < valid_rows;
-    const __nv_bfloat16* src = gbase + (ok ? int64_t(r) * stride : 0) + c * 8;
-    cp_async16(smem_tile + tile_off(r, c), src, ok ? 16 : 0);
+  constexpr int RPP = THREADS / 8;  // rows per pass of the CTA
+  if constexpr (RPP % 8 == 0) {
+    // a thread keeps its 16-byte column and its row modulo 8 from pass to pass: the swizzle term
+    // is fixed and both addresses advance by constants
+    const int r0 = threadIdx.x >> 3, c = threadIdx.x & 7;
+    uint32_t dst = smem_tile + tile_off(r0, c);
+    const __nv_bfloat16* src = gbase + int64_t(r0) * stride + c * 8;
+    for (int r = r0; r < rows; r += RPP, dst += RPP * 128, src += RPP * stride) {
+      const bool ok = r < valid_rows;
+      cp_async16(dst, ok ? src : gbase, ok ? 16 : 0);
+    }
+  } else {
+    for (int i = threadIdx.x; i < rows * 8; i += THREADS) {
+      const int r = i >> 3, c = i & 7;
+      const bool ok = r < valid_rows;
+      const __nv_bfloat16* src = gbase + (ok ? int64_t(r) * stride : 0) + c * 8;
+      cp_async16(smem_tile + tile_off(r, c), src, ok ? 16 : 0);
+    }
   }
 }
 
@@ -270,12 +283,16 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
     // resource of this kernel, and a 30-token query fills two of a tile's four blocks.
     const int nkb = min(4, (kv_hi - k0 + 15) >> 4);
 
-    // S = Q K^T for this warp's 16 rows x 64 keys
+    // S = Q K^T for this warp's 16 rows x 64 keys.  Everything from here to P V touches only the
+    // nkb 16-key blocks in use (s[2 jp], s[2 jp + 1] for jp < nkb): the rest of a short sequence's
+    // tile would be scaled, masked to -inf, exponentiated to 0 and added, instruction by instruction.
     float s[8][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int jp = 0; jp < 4; ++jp) {
+      if (jp >= nkb) break;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+      for (int e = 0; e < 4; ++e) s[2 * jp][e] = s[2 * jp + 1][e] = 0.f;
+    }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
@@ -291,21 +308,29 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
       }
     }
 
-    // scale into the exp2 domain and mask
-    const bool need_mask = (half_window >= 0) || (k0 + ATT_BN > kv_hi);
+    // scale into the exp2 domain and mask.  A band as wide as the sequence excludes nothing.
+    const bool band = half_window >= 0 && half_window < len - 1;
+    const bool need_mask = band || (k0 + ATT_BN > kv_hi);
+    const int lim = kv_hi - k0 - (lane & 3) * 2;  // column 8 j + (e & 1) of this lane is a key of the sequence iff < lim
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int jp = 0; jp < 4; ++jp) {
+      if (jp >= nkb) break;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float v = s[j][e] * scale_log2;
-        if (need_mask) {
-          const int key = k0 + j * 8 + (lane & 3) * 2 + (e & 1);
-          const int qi = qrow0 + (e >> 1) * 8;
-          bool ok = key < kv_hi;
-          if (half_window >= 0) ok = ok && (abs(qi - key) <= half_window);
-          if (!ok) v = -INFINITY;
+      for (int j = 2 * jp; j < 2 * jp + 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s[j][e] * scale_log2;
+          if (need_mask) {
+            bool ok = j * 8 + (e & 1) < lim;
+            if (band) {
+              const int key = k0 + j * 8 + (lane & 3) * 2 + (e & 1);
+              const int qi = qrow0 + (e >> 1) * 8;
+              ok = ok && (abs(qi - key) <= half_window);
+            }
+            if (!ok) v = -INFINITY;
+          }
+          s[j][e] = v;
         }
-        s[j][e] = v;
       }
     }
     // online softmax for rows r (e = 0,1) and r + 8 (e = 2,3)
@@ -313,30 +338,41 @@ attn_varlen_mma_kernel(const __nv_bfloat16* __restrict__ qkv, const int4* __rest
     for (int h2 = 0; h2 < 2; ++h2) {
       float mx = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fmaxf(s[j][h2 * 2], s[j][h2 * 2 + 1]));
+      for (int jp = 0; jp < 4; ++jp) {
+        if (jp >= nkb) break;
+        mx = fmaxf(mx, fmaxf(fmaxf(s[2 * jp][h2 * 2], s[2 * jp][h2 * 2 + 1]),
+                             fmaxf(s[2 * jp + 1][h2 * 2], s[2 * jp + 1][h2 * 2 + 1])));
+      }
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_new = fmaxf(m_run[h2], mx);
       const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = fast_exp2(m_run[h2] - m_safe);
       float sum = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float p0 = fast_exp2(s[j][h2 * 2] - m_safe);
-        const float p1 = fast_exp2(s[j][h2 * 2 + 1] - m_safe);
-        s[j][h2 * 2] = p0;
-        s[j][h2 * 2 + 1] = p1;
-        sum += p0 + p1;
+      for (int jp = 0; jp < 4; ++jp) {
+        if (jp >= nkb) break;
+#pragma unroll
+        for (int j = 2 * jp; j < 2 * jp + 2; ++j) {
+          const float p0 = fast_exp2(s[j][h2 * 2] - m_safe);
+          const float p1 = fast_exp2(s[j][h2 * 2 + 1] - m_safe);
+          s[j][h2 * 2] = p0;
+          s[j][h2 * 2 + 1] = p1;
+          sum += p0 + p1;
+        }
       }
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      l_run[h2] = l_run[h2] * alpha + sum;
-      m_run[h2] = m_new;
+      if (it > 0) {  // a first tile has nothing to rescale
+        const float alpha = fast_exp2(m_run[h2] - m_safe);
+        l_run[h2] *= alpha;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        o_acc[j][h2 * 2] *= alpha;
-        o_acc[j][h2 * 2 + 1] *= alpha;
+        for (int j = 0; j < 8; ++j) {
+          o_acc[j][h2 * 2] *= alpha;
+          o_acc[j][h2 * 2 + 1] *= alpha;
+        }
       }
+      l_run[h2] += sum;
+      m_run[h2] = m_new;
     }
     // O += P V
 #pragma unroll
