@@ -57,6 +57,20 @@ def test_short_query_tiles(pe, cuda_device, lengths, half_window):
     _check(out, qkv, cu, half_window, f"short {lengths}")
 
 
+@pytest.mark.parametrize("n_heads", [1, 3, 6, 28])
+def test_short_tiles_shared_among_heads(pe, cuda_device, n_heads):
+    """A sequence of at most 16 (32) tokens shares its 64-row tile among four (two) heads, four heads
+    to a CTA: head counts that leave slots of the last step empty (1, 3, 6) and one that fills
+    several CTAs per tile (28), lengths on both sides of 16 / 32 / 48, with and without a band."""
+    lengths = [1, 15, 16, 17, 31, 32, 33, 47, 48, 49, 64, 9, 24]
+    qkv, cu = _qkv(lengths, n_heads, cuda_device, seed=31)
+    for hw in (None, 64, 5):
+        _check(_run(qkv, cu, n_heads, hw, cuda_device), qkv, cu, hw, f"shared tiles heads={n_heads} window={hw}")
+    short = [l for l in lengths if l <= 32]
+    qkv, cu = _qkv(short, n_heads, cuda_device, seed=32)      # 32-row tiles: two heads per step at most
+    _check(_run(qkv, cu, n_heads, None, cuda_device), qkv, cu, None, f"shared 32-row tiles heads={n_heads}")
+
+
 def test_small_window_and_long_sequence(pe, cuda_device):
     qkv, cu = _qkv([2048, 5, 900], 2, cuda_device, seed=2)
     for hw in (None, 64, 8):
